@@ -1,0 +1,107 @@
+"""ctypes binding of libvlgpu.so, the C-ABI library holding the sm_100a kernels.
+
+There is no CPU fallback: if the library is missing or a call is rejected, an exception is
+raised.  Entry points and their argument meaning are declared in include/vlgpu.h.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libvlgpu.so")
+
+c_i32p = ctypes.POINTER(ctypes.c_int32)
+c_f32p = ctypes.POINTER(ctypes.c_float)
+c_u8p = ctypes.POINTER(ctypes.c_uint8)
+c_u32p = ctypes.POINTER(ctypes.c_uint32)
+c_intp = ctypes.POINTER(ctypes.c_int)
+
+EXPORTS = [
+    "vl_last_error", "vl_abi_version", "vl_calculate_distances", "vl_search_from_seeds", "vl_queue_insert",
+    "vl_queue_pop", "vl_punchout_excluded", "vl_dedup_adjacent", "vl_sort_pairs", "vl_dedup_sort_ids",
+    "vl_seen_add", "vl_prune", "vl_beam_search", "vl_beam_search_plan",
+]
+
+
+class BeamParams(ctypes.Structure):
+    """Mirror of `vl_beam_params` (include/vlgpu.h)."""
+    _fields_ = [
+        ("vectors", ctypes.c_void_p), ("n", ctypes.c_int64), ("dim", ctypes.c_int32), ("metric", ctypes.c_int32),
+        ("graph", ctypes.c_void_p), ("graph_w", ctypes.c_int32), ("pvc", ctypes.c_int32),
+        ("queries", ctypes.c_void_p), ("rows", ctypes.c_int64),
+        ("seed_ids", ctypes.c_void_p), ("seed_dist", ctypes.c_void_p), ("seed_ld", ctypes.c_int64),
+        ("seed_cols", ctypes.c_int32), ("sq_len", ctypes.c_int32), ("vq_len", ctypes.c_int32),
+        ("seen_cap", ctypes.c_int32),
+        ("out_ids", ctypes.c_void_p), ("out_dist", ctypes.c_void_p), ("out_ld", ctypes.c_int64),
+        ("out_cols", ctypes.c_int32), ("n_iters", ctypes.c_int32), ("readahead", ctypes.c_int32),
+        ("dump_last", ctypes.c_int32), ("exclude_w", ctypes.c_int32),
+        ("exclude", ctypes.c_void_p), ("self_base", ctypes.c_int64), ("group_rows", ctypes.c_int64),
+        ("changed_flags", ctypes.c_void_p), ("n_checks", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("group_full", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
+_lib = None
+
+
+class VlError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it was not built (python vectorlink-gpu_b200/build.py)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise VlError(f"{LIB_PATH} is missing: build it with `python vectorlink-gpu_b200/build.py` "
+                          "(there is no CPU fallback)")
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.vl_last_error.restype = ctypes.c_char_p
+        for name in EXPORTS[1:]:
+            getattr(_lib, name).restype = ctypes.c_int
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise VlError(f"{what} failed ({rc}): {lib().vl_last_error().decode()}")
+
+
+def ptr(t):
+    """Device address of a tensor (None -> NULL)."""
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def stream_of(t: torch.Tensor):
+    """torch's current stream on the tensor's device, as the void* the C ABI takes."""
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise VlError("vectorlink_gpu runs on CUDA tensors only (there is no CPU path); got a tensor on "
+                          f"{t.device}")
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """One int32 per device that kernels OR VL_STATUS_* bits into."""
+    key = torch.device(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _status[key]
+
+
+def read_status(device) -> int:
+    """Reads and clears the status word (a device sync)."""
+    s = status_word(device)
+    v = int(s.item())
+    if v:
+        s.zero_()
+    return v
