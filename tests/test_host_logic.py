@@ -1,0 +1,61 @@
+"""Host-side driver logic that needs no GPU."""
+import numpy as np
+import torch
+
+import oracle
+
+
+def cfg(**kw):
+    return oracle.make_config(**kw)
+
+
+def test_loop_bounds_match_the_oracle_iteration_counts(c1, small):
+    from vectorlink_gpu.ann import loop_bounds
+    from conftest import cfg_of
+    for g in (c1,):
+        config, _ = cfg_of(g)
+        q = oracle.initial_search_queue(g["vectors"], g["queries"], config)
+        n = oracle.closest_vectors(g["queries"], q, g["vectors"], g["beams"], config)
+        k_none, n_checks, n_max = loop_bounds(config)
+        assert n == n_max and k_none <= n_max and n_checks == k_none // config["speculative_readahead"]
+
+
+def test_loop_bounds_closed_form():
+    from vectorlink_gpu.ann import loop_bounds
+    assert loop_bounds(cfg(beam_size=16)) == (61, 12, 65)                       # E=240: 61 productive, leaves at 65
+    assert loop_bounds(cfg(beam_size=32, visit_queue_factor=2)) == (81, 16, 85)  # E=320
+    assert loop_bounds(cfg(beam_size=64, visit_queue_factor=2)) == (161, 32, 165)
+    assert loop_bounds(cfg(beam_size=8, exclude_factor=0)) == (1, 0, 5)
+    k_none, n_checks, n_max = loop_bounds(cfg(beam_size=6, visit_queue_factor=1, exclude_factor=6, parallel_visit_count=4))
+    assert (k_none, n_checks, n_max) == (10, 2, 15)                              # k_none on a check iteration
+
+
+def test_natural_end_reads_the_first_quiet_check():
+    from vectorlink_gpu.ann import _natural_end
+    config = cfg(beam_size=16)
+    assert _natural_end([1] * 12, config) == 65
+    assert _natural_end([1, 1, 0] + [1] * 9, config) == 15
+    assert _natural_end([0] * 12, config) == 5
+
+
+def test_fused_shape_rule():
+    from vectorlink_gpu.ann import _fused_shape_ok
+    v = torch.zeros(8, 64)
+    c = cfg(beam_size=16)
+    assert _fused_shape_ok(v, 48, 48, 48 + 4 * 48, c)            # build queue
+    assert _fused_shape_ok(v, 16, 48, 48 + 64, c)                # search queue (Q=48, pvc*D=64)
+    assert not _fused_shape_ok(v, 16, 96, 192, cfg(beam_size=16, recall_search_queue_factor=6))  # stale columns
+    assert not _fused_shape_ok(torch.zeros(8, 30), 48, 48, 240, c)  # rows not 16-byte chunks
+
+
+def test_seed_table_equals_the_oracle_table():
+    from vectorlink_gpu.constants import PRIMES_HOST, MAXINT, MAXFLOAT
+    assert np.array_equal(PRIMES_HOST.numpy(), oracle.primes_table())
+    assert MAXINT == oracle.MAXINT and float(np.float32(MAXFLOAT)) == oracle.MAXFLOAT
+
+
+def test_readme_alias_imports():
+    import vectorlink
+    from vectorlink.ann import ANN
+    from vectorlink_gpu import ANN as ANN2
+    assert ANN is ANN2

@@ -1,0 +1,128 @@
+"""The C oracle against the committed outputs of the reference's own code (CPU only)."""
+import numpy as np
+import pytest
+
+import oracle
+from conftest import cfg_of
+
+MAXINT = oracle.MAXINT
+
+
+@pytest.mark.parametrize("dim", [64, 96, 128, 768, 1024, 1536])
+def test_calculate_distances_matches_simulated_reference_kernel(kat, dim):
+    d = oracle.calculate_distances(kat[f"k4_{dim}_vectors"], kat[f"k4_{dim}_beams"])
+    assert np.array_equal(d, kat[f"k4_{dim}_out"])  # bit for bit
+
+
+@pytest.mark.parametrize("dim", [1024, 1536])
+def test_search_from_seeds_matches_simulated_reference_kernel(kat, dim):
+    i, d = oracle.search_from_seeds(kat[f"k5_{dim}_queries"], kat[f"k5_{dim}_visit"], kat[f"k5_{dim}_beams"],
+                                    kat[f"k5_{dim}_vectors"])
+    assert np.array_equal(i, kat[f"k5_{dim}_idx"])
+    assert np.array_equal(d, kat[f"k5_{dim}_dist"])
+
+
+def test_queue_sort_matches_simulated_dedup(kat):
+    i, d = oracle.queue_sort(kat["k67_ids_in"], kat["k67_dist_in"])
+    assert np.array_equal(i, kat["k67_sorted_ids_out"])
+    assert np.array_equal(d, kat["k67_sorted_dist_out"])
+
+
+def test_dedup_sort_matches_simulated_dedup(kat):
+    want = np.sort(kat["k68_out"], axis=1)
+    assert np.array_equal(oracle.dedup_sort(kat["k68_in"]), want)
+
+
+def test_punchout_excluded_on_views(kat):
+    ids, dist = kat["k10_ids_in"].copy(), kat["k10_dist_in"].copy()
+    c0 = int(kat["k10_col0"])
+    oracle.punchout_excluded_(ids[:, c0:], dist[:, c0:], kat["k10_excl"])
+    assert np.array_equal(ids, kat["k10_ids_out"])
+    assert np.array_equal(dist, kat["k10_dist_out"])
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_prune_matches_simulated_reference_kernel(kat, tag):
+    b, d = oracle.prune_(kat[f"k9{tag}_beams_in"], kat[f"k9{tag}_dist_in"])
+    assert np.array_equal(b, kat[f"k9{tag}_beams_out"])
+    assert np.array_equal(d, kat[f"k9{tag}_dist_out"])
+    assert (b == MAXINT).sum() > (kat[f"k9{tag}_beams_in"] == MAXINT).sum()  # something was pruned
+
+
+def test_prime_table_layout():
+    t = oracle.primes_table()
+    assert t.shape == (965,) and t[0] == 10000349 and t[583] == 10009729 and t[584] == 1009007
+    assert list(t[659:664]) == [1, 2, 59063, 79193, 3] and t[-1] == 1999
+
+
+def test_queue_operator_trace(c1):
+    q = oracle.Queue(6, 12, 28)
+    q.insert(c1["op_ins0_ids"], c1["op_ins0_dist"])
+    assert np.array_equal(q.indices, c1["op_q0_ids"]) and np.array_equal(q.distances, c1["op_q0_dist"])
+    popped = q.pop_n_ids(3)
+    assert np.array_equal(popped, c1["op_pop_ids"])
+    assert np.array_equal(q.indices, c1["op_q1_ids"]) and np.array_equal(q.distances, c1["op_q1_dist"])
+    changed = q.insert(c1["op_ins1_ids"], c1["op_ins1_dist"], exclude=c1["op_ins1_excl"], output_update=True)
+    assert np.array_equal(q.indices, c1["op_q2_ids"]) and np.array_equal(q.distances, c1["op_q2_dist"])
+    assert np.array_equal(changed, c1["op_q2_changed"])
+
+
+def test_seen_list_trace(c1):
+    seen = np.full((4, 7), MAXINT, dtype=np.int32)
+    for vis, want, alive in zip(c1["op_seen_visits"], c1["op_seen_trace"], c1["op_seen_alive"]):
+        r = oracle.add_new_to_seen_(seen, vis) if seen is not None else None
+        assert (r is not None) == bool(alive)
+        if r is None:
+            seen = None
+        else:
+            assert np.array_equal(seen, want)
+
+
+def test_circulants(c1):
+    p = oracle.primes_table(9)
+    assert np.array_equal(oracle.circulants(50, 50, p), c1["op_circ_beams"])
+    assert np.array_equal(oracle.circulants(7, 50, p), c1["op_circ_queue"])
+
+
+@pytest.mark.parametrize("which", ["c1", "small"])
+def test_build_matches_reference_host_code(which, c1, small):
+    g = c1 if which == "c1" else small
+    cfg, _ = cfg_of(g)
+    beams, dist, loops, found = oracle.generate_ann(g["vectors"], cfg)
+    assert np.array_equal(beams, g["beams"])
+    assert np.array_equal(dist, g["distances"])        # distances of the final neighbour lists
+    assert found == int(g["self_recall_found"])
+
+
+@pytest.mark.parametrize("which", ["c1", "small"])
+def test_search_matches_reference_host_code(which, c1, small):
+    g = c1 if which == "c1" else small
+    cfg, _ = cfg_of(g)
+    sq = oracle.search(g["vectors"], g["beams"], g["queries"], cfg)
+    assert sq.length == int(g["search_length"])
+    # reference with its seed distances summed in the kernels' order: bit for bit
+    assert np.array_equal(sq.indices, g["search_tree_ids"])
+    assert np.array_equal(sq.distances, g["search_tree_dist"])
+    # reference exactly as shipped (torch-order seed sum, no clamp): ids equal, distances within 1e-5
+    assert np.array_equal(sq.indices, g["search_ids"])
+    real = g["search_ids"] != MAXINT
+    assert np.allclose(sq.distances[real], g["search_dist"][real], rtol=1e-5, atol=1e-7)
+    one = oracle.search(g["vectors"], g["beams"], g["queries"][:1], cfg)
+    assert np.array_equal(one.indices, g["search1_ids"])    # un-patched single-query reference call
+
+
+def test_recall_of_the_reference_graph(c1):
+    cfg, _ = cfg_of(c1)
+    sq = oracle.search(c1["vectors"], c1["beams"], c1["queries"], cfg)
+    truth = oracle.bruteforce_knn(c1["vectors"], c1["queries"], 10)
+    hits = sum(len(set(sq.indices[i, :10]) & set(truth[i])) for i in range(truth.shape[0]))
+    assert hits / truth.size >= 0.95
+
+
+def test_sql2_tree_is_exact_on_integer_data():
+    rng = np.random.default_rng(0)
+    v = rng.integers(0, 256, size=(50, 128)).astype(np.float32)
+    ids = rng.integers(0, 50, size=(50, 4)).astype(np.int32)
+    d = oracle.calculate_distances(v, ids, metric="l2")
+    want = ((v[:, None, :].astype(np.float64) - v[ids].astype(np.float64)) ** 2).sum(-1)
+    assert np.array_equal(d.astype(np.float64), want)

@@ -62,6 +62,19 @@ def lib() -> ctypes.CDLL:
         _lib.vl_last_error.restype = ctypes.c_char_p
         for name in EXPORTS[1:]:
             getattr(_lib, name).restype = ctypes.c_int
+        P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+        _lib.vl_calculate_distances.argtypes = [P, L, I, P, L, P, I, P, I, P, P]
+        _lib.vl_search_from_seeds.argtypes = [P, L, P, I, P, I, P, L, I, P, P, I, P, P]
+        _lib.vl_queue_insert.argtypes = [P, P, L, I, I, P, P, I, P, I, P, P]
+        _lib.vl_queue_pop.argtypes = [P, P, L, I, I, I, P, P]
+        _lib.vl_punchout_excluded.argtypes = [P, P, L, L, L, I, P, I, P]
+        _lib.vl_dedup_adjacent.argtypes = [P, P, L, I, P]
+        _lib.vl_sort_pairs.argtypes = [P, P, L, I, I, P]
+        _lib.vl_dedup_sort_ids.argtypes = [P, L, I, P]
+        _lib.vl_seen_add.argtypes = [P, L, I, P, I, P, P, P]
+        _lib.vl_prune.argtypes = [P, P, L, I, I, P, P, I, P, P]
+        _lib.vl_beam_search.argtypes = [ctypes.POINTER(BeamParams), P]
+        _lib.vl_beam_search_plan.argtypes = [ctypes.POINTER(BeamParams), c_intp, c_intp, c_intp]
     return _lib
 
 

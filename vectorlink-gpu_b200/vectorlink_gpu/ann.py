@@ -1,0 +1,457 @@
+"""ANN graph build and beam search with the reference's driver API (vectorlink_gpu/ann.py).
+
+`closest_vectors` runs the whole budgeted search of a batch as one fused kernel
+(csrc/vl_beam.cu) whenever the queue shapes allow it, and otherwise steps through the
+reference's loop with the operator-level kernels.  Both produce the reference's queues.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import subprocess
+import time
+from typing import Dict, List, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import BeamParams, check, lib, ptr, stream_of
+from .constants import MAXFLOAT, MAXINT
+from .kernels import calculate_distances, metric_code, prune_, search_from_seeds, sort_pairs_
+from .log import log_time
+from . import log as _log
+from .queue import Queue
+from .utils import add_new_to_seen_, generate_circulant_beams, generate_queue_circulants, primes
+
+FUSED_MAX_SMEM_PER_ROW = 200 * 1024
+
+
+def _metric_of(config: Dict):
+    return config.get("metric", "cosine")
+
+
+def _fused_shape_ok(vectors: Tensor, beam_w: int, sq_len: int, sq_cap: int, config: Dict) -> bool:
+    """The fused kernel models a queue as "the `length` best of head + candidates", which is
+    what Queue.insert computes when capacity == length + candidates per iteration."""
+    pvc = config["parallel_visit_count"]
+    vq_len = config["visit_queue_factor"] * config["beam_size"]
+    m = pvc * beam_w
+    e = config["exclude_factor"] * vq_len
+    smem = 8 * m + 16 * sq_len + 16 * vq_len + 4 * 4 * max(e, 16) + 512
+    return (vectors.size(1) % 4 == 0 and vectors.data_ptr() % 16 == 0 and 1 <= pvc <= 32 and pvc <= vq_len
+            and sq_cap == sq_len + m and sq_len <= 4096 and smem <= FUSED_MAX_SMEM_PER_ROW
+            and config["speculative_readahead"] >= 1)
+
+
+def loop_bounds(config: Dict) -> Tuple[int, int, int]:
+    """(k_none, n_checks, n_max) of the reference loop (ann.py:66-91, utils.py:61-82) for a
+    batch in which some row always pops real ids: `seen` takes pvc ids per iteration and is
+    found full at iteration k_none = ceil(E/pvc)+1; from then on nothing changes, so the loop
+    leaves at the first multiple of speculative_readahead after k_none (n_max) unless an
+    earlier check saw no change; n_checks = checks at or before k_none."""
+    pvc = config["parallel_visit_count"]
+    e = config["exclude_factor"] * config["visit_queue_factor"] * config["beam_size"]
+    ra = config["speculative_readahead"]
+    k_none = (e + pvc - 1) // pvc + 1
+    n_checks = k_none // ra
+    n_max = (k_none // ra + 1) * ra
+    return k_none, n_checks, n_max
+
+
+def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
+                 config, n_iters, dump_last, exclude, self_base, group_rows, flags, full):
+    pvc = config["parallel_visit_count"]
+    vq_len = config["visit_queue_factor"] * config["beam_size"]
+    p = BeamParams()
+    p.vectors = vectors.data_ptr()
+    p.n = vectors.size(0)
+    p.dim = vectors.size(1)
+    p.metric = metric_code(_metric_of(config))
+    p.graph = graph.data_ptr()
+    p.graph_w = graph.size(1)
+    p.pvc = pvc
+    p.queries = queries.data_ptr()
+    p.rows = queries.size(0)
+    p.seed_ids = seed_ids.data_ptr()
+    p.seed_dist = seed_dist.data_ptr()
+    p.seed_ld = seed_ids.stride(0)
+    p.seed_cols = seed_cols
+    p.sq_len = sq_len
+    p.vq_len = vq_len
+    p.seen_cap = config["exclude_factor"] * vq_len
+    p.out_ids = out_ids.data_ptr()
+    p.out_dist = out_dist.data_ptr()
+    p.out_ld = out_ids.stride(0)
+    p.out_cols = out_cols
+    p.n_iters = n_iters
+    p.readahead = config["speculative_readahead"]
+    p.dump_last = 1 if dump_last else 0
+    p.exclude_w = exclude.size(1) if exclude is not None else 0
+    p.exclude = exclude.data_ptr() if exclude is not None else 0
+    p.self_base = self_base
+    p.group_rows = group_rows
+    p.changed_flags = flags.data_ptr()
+    p.n_checks = flags.size(1)
+    p.group_full = full.data_ptr()
+    p.status = _lib.status_word(vectors.device).data_ptr()
+    check(lib().vl_beam_search(ctypes.byref(p), stream_of(vectors)), "vl_beam_search")
+
+
+def _natural_end(flag_row: List[int], config: Dict) -> int:
+    """Iteration at which the reference loop leaves, given the per-check "any head changed"."""
+    k_none, n_checks, n_max = loop_bounds(config)
+    ra = config["speculative_readahead"]
+    for c in range(n_checks):
+        if not flag_row[c]:
+            return (c + 1) * ra
+    return n_max
+
+
+def _fused_batches(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, sq_cap, config, exclude,
+                   self_base, group_rows, out_ids, out_dist, out_cols, stepwise):
+    """Runs the fused search over `queries` split in batches of `group_rows` (the reference's
+    host loop, ann.py:132-166) in one launch, then repairs the batches for which the
+    reference's batch-wide decisions differ from the budgeted schedule: a batch whose heads
+    stopped changing at an earlier check is re-run up to that iteration, a batch in which
+    every row popped a MAXINT at some point goes through `stepwise`.  Returns the iteration
+    count of every batch."""
+    rows = queries.size(0)
+    k_none, n_checks, n_max = loop_bounds(config)
+    groups = (rows + group_rows - 1) // group_rows if rows else 0
+    dev = vectors.device
+    flags = torch.zeros((max(groups, 1), max(n_checks, 1)), dtype=torch.int32, device=dev)
+    full = torch.zeros((max(groups, 1),), dtype=torch.int32, device=dev)
+    if rows == 0:
+        return []
+    _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
+                 config, n_max, False, exclude, self_base, group_rows, flags, full)
+    flags_h = flags.cpu().tolist()
+    full_h = full.cpu().tolist()
+    counts = []
+    for gi in range(groups):
+        lo, hi = gi * group_rows, min(rows, (gi + 1) * group_rows)
+        end = _natural_end(flags_h[gi][:n_checks], config) if n_checks else n_max
+        if not full_h[gi]:
+            counts.append(stepwise(lo, hi))
+            continue
+        counts.append(end)
+        if end > k_none:
+            continue
+        # the reference left at check iteration `end`: redo the batch up to it; the last insert
+        # is a whole-row sort so that the columns behind `length` match too
+        tmp_i = torch.empty((hi - lo, sq_cap), dtype=torch.int32, device=dev)
+        tmp_d = torch.empty((hi - lo, sq_cap), dtype=torch.float32, device=dev)
+        f2 = torch.zeros((1, max(n_checks, 1)), dtype=torch.int32, device=dev)
+        u2 = torch.zeros((1,), dtype=torch.int32, device=dev)
+        _launch_beam(vectors, graph, queries[lo:hi], seed_ids[lo:hi], seed_dist[lo:hi], seed_cols, sq_len, tmp_i, tmp_d,
+                     sq_cap, config, end, True, exclude[lo:hi] if exclude is not None else None,
+                     self_base + lo if self_base >= 0 else -1, hi - lo, f2, u2)
+        sort_pairs_(tmp_i, tmp_d, dedup=True)
+        out_ids[lo:hi, :out_cols].copy_(tmp_i[:, :out_cols])
+        out_dist[lo:hi, :out_cols].copy_(tmp_d[:, :out_cols])
+    return counts
+
+
+def closest_vectors_stepwise(query_vecs: Tensor, search_queue: Queue, vectors: Tensor, beams: Tensor, config: Dict,
+                             exclude: Optional[Tensor] = None) -> int:
+    """ann.py:37-93 step by step with the operator-level kernels (any queue shape)."""
+    metric = _metric_of(config)
+    (beam_count, beam_size) = beams.size()
+    extra_capacity = beam_size * config["parallel_visit_count"]
+    (batch_size, queue_capacity) = search_queue.size()
+    visit_queue_len = config["visit_queue_factor"] * config["beam_size"]
+    capacity = visit_queue_len + extra_capacity
+    visit_queue = Queue(batch_size, visit_queue_len, capacity, device=vectors.device)
+    visit_queue.initialize_from_queue(search_queue)
+    exclude_len = config["exclude_factor"] * visit_queue_len
+    seen = torch.full((batch_size, exclude_len), MAXINT, dtype=torch.int32, device=vectors.device)
+    progressing = True
+    count = 0
+    while progressing:
+        count += 1
+        checking_output = (count % config["speculative_readahead"]) == 0
+        neighbors_to_visit = visit_queue.pop_n_ids(config["parallel_visit_count"])
+        (indexes_of_comparisons, distances_of_comparisons) = search_from_seeds(
+            query_vecs, neighbors_to_visit, beams, vectors, metric=metric)
+        did_something = search_queue.insert(indexes_of_comparisons, distances_of_comparisons, exclude=exclude,
+                                            output_update=checking_output)
+        if seen is not None:
+            seen = add_new_to_seen_(seen, neighbors_to_visit)
+        if seen is not None:
+            visit_queue.insert(indexes_of_comparisons, distances_of_comparisons, exclude=seen)
+        if checking_output:
+            progressing = bool(torch.any(did_something))
+    return count
+
+
+@log_time
+def closest_vectors(query_vecs: Tensor, search_queue: Queue, vectors: Tensor, beams: Tensor, config: Dict,
+                    exclude: Optional[Tensor] = None):
+    """ann.py:37-93: beam search of every row of `query_vecs` through the graph `beams`,
+    starting from and updating `search_queue`.  Returns True like the reference; the number
+    of loop iterations the reference would have run is kept in `closest_vectors.last_count`."""
+    _lib.require_cuda(query_vecs, vectors, beams, search_queue.indices)
+    assert query_vecs.is_contiguous() and vectors.is_contiguous() and beams.is_contiguous()
+    (batch_size, queue_capacity) = search_queue.size()
+    sq_len = search_queue.length
+    force_stepwise = bool(config.get("stepwise", False))
+    if force_stepwise or not _fused_shape_ok(vectors, beams.size(1), sq_len, queue_capacity, config) or batch_size == 0:
+        closest_vectors.last_count = closest_vectors_stepwise(query_vecs, search_queue, vectors, beams, config, exclude)
+        return True
+    if exclude is not None:
+        exclude = exclude.contiguous()
+        assert exclude.dtype == torch.int32 and exclude.size(0) == batch_size
+    in_ids, in_dist = search_queue.indices, search_queue.distances
+    out_ids = torch.empty_like(in_ids)
+    out_dist = torch.empty_like(in_dist)
+
+    def stepwise(lo, hi):
+        assert lo == 0 and hi == batch_size
+        q = Queue(batch_size, sq_len, queue_capacity, device=vectors.device)
+        q.indices.copy_(in_ids)
+        q.distances.copy_(in_dist)
+        n = closest_vectors_stepwise(query_vecs, q, vectors, beams, config, exclude)
+        out_ids.copy_(q.indices)
+        out_dist.copy_(q.distances)
+        return n
+
+    counts = _fused_batches(vectors, beams, query_vecs, in_ids, in_dist, sq_len, sq_len, queue_capacity, config,
+                            exclude, -1, batch_size, out_ids, out_dist, queue_capacity, stepwise)
+    search_queue.indices = out_ids
+    search_queue.distances = out_dist
+    closest_vectors.last_count = counts[0]
+    return True
+
+
+closest_vectors.last_count = 0
+
+
+def search_layers(layers: List[Tensor], query_vecs: Tensor, search_queue: Queue, vectors: Tensor, config: Dict):
+    """ann.py:96-106."""
+    for layer in layers:
+        closest_vectors(query_vecs, search_queue, vectors, layer, config, None)
+
+
+def excluding_self(start, end, queue_length, device="cuda"):
+    """ann.py:315-320: one exclusion list per row holding the row's own id."""
+    return torch.arange(start, end, dtype=torch.int32, device=device).unsqueeze(1).contiguous()
+
+
+def generate_ann(vectors: Tensor, config: Dict) -> Tuple[Tensor, Tensor]:
+    """ann.py:109-193: circulant start graph of width W = beam_size * beam_queue_factor, then up
+    to `optimization_loops` rounds of: beam-search every node from its current neighbours
+    (batch by batch in the reference; all batches in one launch here, since a batch only
+    reads the previous round's graph), detour prune, self-recall check.
+    Departures from the reference, both where its own result is accidental: the distances
+    carried into the next round and returned are those of the neighbour lists (the reference
+    keeps the initial circulant distances, ann.py:172 assigns to an unused name), and a
+    MAXINT neighbour yields sentinels instead of an out-of-range read."""
+    _lib.require_cuda(vectors)
+    (num_vecs, vec_dim) = vectors.size()
+    beam_size = config["beam_size"]
+    queue_length = beam_size * config["beam_queue_factor"]
+    dev = vectors.device
+    metric = _metric_of(config)
+    neighbor_primes = primes(queue_length, dev)
+    beams = generate_circulant_beams(num_vecs, neighbor_primes)
+    assert beams.dtype == torch.int32
+    beam_distances = calculate_distances(vectors, beams, metric=metric)
+    remaining_capacity = queue_length * config["parallel_visit_count"]
+    capacity = queue_length + remaining_capacity
+    batch_size = config["batch_size"]
+    fused = not config.get("stepwise", False) and _fused_shape_ok(vectors, queue_length, queue_length, capacity, config)
+    loops_run = 0
+    for i in range(0, config["optimization_loops"]):
+        print_timestamp(f"start of cagra loop {i}")
+        next_beams = torch.empty_like(beams)
+        next_beam_distances = torch.empty_like(beam_distances)
+
+        def batch_stepwise(lo, hi):
+            exclude = excluding_self(lo, hi, queue_length, dev)
+            queue = Queue(hi - lo, queue_length, capacity, device=dev)
+            queue.insert(beams.narrow(0, lo, hi - lo), beam_distances.narrow(0, lo, hi - lo))
+            n = closest_vectors_stepwise(vectors[lo:hi], queue, vectors, beams, config, exclude)
+            next_beams.narrow(0, lo, hi - lo).copy_(queue.indices.narrow(1, 0, queue_length))
+            next_beam_distances.narrow(0, lo, hi - lo).copy_(queue.distances.narrow(1, 0, queue_length))
+            return n
+
+        if fused:
+            _fused_batches(vectors, beams, vectors, beams, beam_distances, queue_length, queue_length, capacity,
+                           config, None, 0, batch_size, next_beams, next_beam_distances, queue_length, batch_stepwise)
+        else:
+            for lo in range(0, num_vecs, batch_size):
+                batch_stepwise(lo, min(num_vecs, lo + batch_size))
+
+        if config["prune"]:
+            (beams, beam_distances) = prune_(next_beams, next_beam_distances)
+        else:
+            (beams, beam_distances) = (next_beams, next_beam_distances)
+        loops_run += 1
+        prefix = min(num_vecs, 1000)
+        (found, recall) = ann_calculate_recall(vectors, beams.narrow_copy(1, 0, beam_size), config,
+                                               sample=vectors[:prefix])
+        if recall == 1.0:
+            break
+        print_timestamp(f"end of cagra loop {i}")
+    generate_ann.last_loops = loops_run
+    return (beams.narrow_copy(1, 0, beam_size), beam_distances.narrow_copy(1, 0, beam_size))
+
+
+generate_ann.last_loops = 0
+
+
+def initial_queue(vectors: Tensor, config: Dict):
+    """ann.py:196-208: circulant seeds among the sample itself."""
+    queue_size = config["recall_search_queue_factor"] * config["beam_size"]
+    (batch_size, _) = vectors.size()
+    extra_capacity = max(queue_size, config["parallel_visit_count"] * config["beam_size"])
+    queue = Queue(batch_size, queue_size, queue_size + extra_capacity, device=vectors.device)
+    p = primes(queue_size, vectors.device)
+    initial_queue_indices = generate_circulant_beams(batch_size, p)
+    d = calculate_distances(vectors, initial_queue_indices, metric=_metric_of(config))
+    queue.insert(initial_queue_indices, d)
+    return queue
+
+
+def query_distances(query_vectors: Tensor, vectors: Tensor, ids: Tensor, metric="cosine") -> Tensor:
+    """Distances of query b to vectors[ids[b, j]] (the role of query_cosine_distances,
+    ann.py:211-214, whose broadcast only works for one query row).  Taken with the same
+    summation order and clamp as every other distance, so a seed that comes back as a
+    candidate carries the same bits; the reference's torch-order sum differs from this by
+    at most an ulp or two."""
+    return calculate_distances(vectors, ids, metric=metric, queries=query_vectors)
+
+
+def initial_search_queue(vectors: Tensor, query_vectors: Tensor, config: Dict):
+    """ann.py:217-232: circulant seeds (b + p_j) mod N for query row b."""
+    queue_size = config["recall_search_queue_factor"] * config["beam_size"]
+    (batch_size, _) = query_vectors.size()
+    extra_capacity = max(queue_size, config["parallel_visit_count"] * config["beam_size"])
+    queue = Queue(batch_size, queue_size, queue_size + extra_capacity, device=vectors.device)
+    p = primes(queue_size, vectors.device)
+    (vector_count, _) = vectors.size()
+    initial_queue_indices = generate_queue_circulants(batch_size, vector_count, p)
+    d = query_distances(query_vectors, vectors, initial_queue_indices, _metric_of(config))
+    queue.insert(initial_queue_indices, d)
+    return queue
+
+
+def ann_calculate_recall(vectors: Tensor, beams: Tensor, config: Dict, sample: Optional[Tensor] = None):
+    """ann.py:235-259: self-recall - rows of the sample whose best hit is themselves."""
+    if sample is None:
+        sample = vectors
+    (sample_size, _) = sample.size()
+    queue = initial_queue(sample.contiguous(), config)
+    closest_vectors(sample.contiguous(), queue, vectors, beams.contiguous(), config)
+    expected = torch.arange(sample_size, device=vectors.device)
+    actual = queue.indices.t()[0]
+    found = (expected == actual).sum().item()
+    print_timestamp(f"found: {found} / {sample_size}")
+    print_timestamp(f"recall: {found / sample_size}")
+    return (found, found / sample_size)
+
+
+def ann_recall_test(vectors: Tensor, config: Dict):
+    """ann.py:287-293."""
+    (beams, _) = generate_ann(vectors, config)
+    prefix = min(vectors.size()[0], 10_000)
+    return ann_calculate_recall(vectors, beams, config, sample=vectors[:prefix])
+
+
+VERBOSE = bool(os.getenv("VECTORLINK_VERBOSE"))
+
+
+def print_timestamp(msg):
+    """ann.py:297-298 prints unconditionally; here only when VECTORLINK_VERBOSE is set."""
+    if VERBOSE:
+        print(msg)
+
+
+class ANN:
+    """ann.py:356-489.  `ANN(vectors=...)` builds the graph; `.beams` int32 [N, beam_size],
+    `.distances` fp32 [N, beam_size], `.search(query)` returns the search `Queue`.
+    Added keyword: metric ("cosine" - the reference's distance on unit vectors - or "l2")."""
+
+    def __init__(self, vectors: Tensor, prune: bool = True, beam_size: int = 24, parallel_visit_count: int = 4,
+                 beam_queue_factor: int = 3, visit_queue_factor: int = 3, exclude_factor: int = 5,
+                 optimization_loops: int = 3, batch_size: int = 10_000, recall_search_queue_factor: int = 3,
+                 speculative_readahead: int = 5, beams: Optional[Tensor] = None, distances: Optional[Tensor] = None,
+                 metric: str = "cosine"):
+        (count, dim) = vectors.size()
+        assert vectors.dtype == torch.float32
+        _lib.require_cuda(vectors)
+        metric_code(metric)
+        self.configuration: Dict = {
+            "prune": prune,
+            "beam_size": beam_size,
+            "parallel_visit_count": parallel_visit_count,
+            "beam_queue_factor": beam_queue_factor,
+            "visit_queue_factor": visit_queue_factor,
+            "exclude_factor": exclude_factor,
+            "optimization_loops": optimization_loops,
+            "batch_size": batch_size,
+            "recall_search_queue_factor": recall_search_queue_factor,
+            "speculative_readahead": speculative_readahead,
+        }
+        if metric != "cosine":
+            self.configuration["metric"] = metric
+        self.vectors = vectors.contiguous()
+        wall_start = time.time()
+        if beams is not None:
+            self.beams = beams
+            if distances is None:
+                self.distances = calculate_distances(self.vectors, self.beams, metric=metric)
+            else:
+                self.distances = distances
+        else:
+            (self.beams, self.distances) = generate_ann(self.vectors, self.configuration)
+        torch.cuda.synchronize(self.vectors.device)
+        wall_end = time.time()
+        total_time: float = wall_end - wall_start
+        self.log = self.configuration.copy()
+        self.log["total_time"] = total_time
+        self.log["vector_count"] = count
+        self.log["vector_dimension"] = dim
+
+    def recall(self, sample_size: int = 1000) -> Tuple[float, float]:
+        """ann.py:456-464."""
+        (count, _) = self.vectors.size()
+        sample_size = min(sample_size, count)
+        sample = self.vectors[0:sample_size]
+        return ann_calculate_recall(self.vectors, self.beams, self.configuration, sample)
+
+    def clusters(self) -> Queue:
+        """ann.py:466-467 is an empty stub; its README says it "returns all search queues":
+        the search queue of every indexed vector, seeded like the recall check
+        (initial_queue) and searched through the graph."""
+        queue = initial_queue(self.vectors, self.configuration)
+        closest_vectors(self.vectors, queue, self.vectors, self.beams, self.configuration)
+        return queue
+
+    def search(self, query: Tensor) -> Queue:
+        """ann.py:469-477: `query` fp32 [B, dim] -> Queue with `.indices` int32 and `.distances`
+        fp32 of shape [B, Q + max(Q, pvc*beam_size)], Q = recall_search_queue_factor*beam_size
+        = `.length`; rows ascending by distance, ids unique, MAXINT/MAXFLOAT padding."""
+        assert query.dtype == torch.float32
+        query = query.contiguous()
+        search_queue = initial_search_queue(self.vectors, query, self.configuration)
+        closest_vectors(query, search_queue, self.vectors, self.beams, self.configuration, None)
+        return search_queue
+
+    def dump_logs(self) -> Dict:
+        """ann.py:479-489."""
+        log = self.log.copy()
+        log["closest_vectors_batch_time"] = _log.CLOSEST_VECTORS_BATCH_TIME
+        try:
+            log["gpu_arch"] = subprocess.check_output(["nvidia-smi", "-L"]).decode("utf-8").strip()
+        except Exception:
+            log["gpu_arch"] = torch.cuda.get_device_name(self.vectors.device)
+        try:
+            log["commit"] = subprocess.check_output(["git", "rev-parse", "--verify", "HEAD"]).decode("utf-8").strip()
+        except Exception:
+            log["commit"] = None
+        (_, recall) = self.recall()
+        log["recall"] = recall
+        return log

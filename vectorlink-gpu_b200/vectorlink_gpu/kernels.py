@@ -1,0 +1,167 @@
+"""Launch wrappers with the reference's operator signatures (vectorlink_gpu/kernels.py).
+
+Each function keeps the name, argument meaning and asserted contracts of the reference
+operator it replaces and calls one entry point of libvlgpu.so on torch's current stream.
+`metric` is the only added argument ("cosine", the reference's distance, or "l2" = squared
+Euclidean).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import check, lib, ptr, stream_of
+from .constants import MAXFLOAT, MAXINT
+from .log import log_time
+
+METRICS = {"cosine": 0, 0: 0, "l2": 1, "sqeuclidean": 1, 1: 1}
+
+
+def metric_code(metric) -> int:
+    try:
+        return METRICS[metric]
+    except KeyError:
+        raise ValueError(f"unknown metric {metric!r}; use 'cosine' or 'l2'") from None
+
+
+@log_time
+def calculate_distances(vectors: Tensor, beams: Tensor, distances_out=None, metric="cosine",
+                        queries: Optional[Tensor] = None) -> Tensor:
+    """kernels.py:174-201: out[i, j] = distance(vectors[i], vectors[beams[i, j]]), MAXFLOAT
+    where beams[i, j] == MAXINT.  `queries` (added) takes the left-hand rows from another
+    matrix: out[i, j] = distance(queries[i], vectors[beams[i, j]])."""
+    assert vectors.dtype == torch.float32
+    assert vectors.is_contiguous()
+    assert beams.dtype == torch.int32
+    assert beams.is_contiguous()
+    q = vectors if queries is None else queries
+    assert q.dtype == torch.float32 and q.is_contiguous()
+    _lib.require_cuda(vectors, beams, q)
+    (vector_count, vector_dimension) = vectors.size()
+    (batches, beam_size) = beams.size()
+    assert batches == q.size(0)
+    assert q.size(1) == vector_dimension
+    if distances_out is None:
+        distances_out = torch.empty((batches, beam_size), dtype=torch.float32, device=vectors.device)
+    else:
+        assert distances_out.is_contiguous() and distances_out.dtype == torch.float32
+    check(lib().vl_calculate_distances(ptr(vectors), ctypes.c_int64(vector_count), vector_dimension, ptr(q),
+                                       ctypes.c_int64(batches), ptr(beams), beam_size, ptr(distances_out),
+                                       metric_code(metric), ptr(_lib.status_word(vectors.device)),
+                                       stream_of(vectors)), "vl_calculate_distances")
+    return distances_out
+
+
+def search_from_seeds(query_vecs: Tensor, neighbors_to_visit: Tensor, beams: Tensor, vectors: Tensor,
+                      metric="cosine") -> Tuple[Tensor, Tensor]:
+    """kernels.py:260-311: ids and distances of the neighbours of the visited nodes, slot
+    v*W + j for visited column v and neighbour slot j; sentinels for a MAXINT visit."""
+    assert query_vecs.dtype == torch.float32
+    assert query_vecs.is_contiguous()
+    assert neighbors_to_visit.dtype == torch.int32
+    assert neighbors_to_visit.is_contiguous()
+    assert beams.dtype == torch.int32
+    assert beams.is_contiguous()
+    assert vectors.is_contiguous()
+    assert vectors.dtype == torch.float32
+    _lib.require_cuda(query_vecs, neighbors_to_visit, beams, vectors)
+    (batch_size, visit_length) = neighbors_to_visit.size()
+    (_, beam_size) = beams.size()
+    (vector_count, vector_dimension) = vectors.size()
+    index_out = torch.empty((batch_size, visit_length * beam_size), dtype=torch.int32, device=vectors.device)
+    distance_out = torch.empty((batch_size, visit_length * beam_size), dtype=torch.float32, device=vectors.device)
+    check(lib().vl_search_from_seeds(ptr(query_vecs), ctypes.c_int64(batch_size), ptr(neighbors_to_visit),
+                                     visit_length, ptr(beams), beam_size, ptr(vectors),
+                                     ctypes.c_int64(vector_count), vector_dimension, ptr(index_out),
+                                     ptr(distance_out), metric_code(metric),
+                                     ptr(_lib.status_word(vectors.device)), stream_of(vectors)),
+          "vl_search_from_seeds")
+    return (index_out, distance_out)
+
+
+def dedup_tensor_(ids: Tensor):
+    """kernels.py:370-380: in place, an id equal to the one before it becomes MAXINT."""
+    assert ids.is_contiguous()
+    assert ids.dtype == torch.int32
+    _lib.require_cuda(ids)
+    (batch_size, queue_size) = ids.size()
+    check(lib().vl_dedup_adjacent(ptr(ids), None, ctypes.c_int64(batch_size), queue_size, stream_of(ids)),
+          "vl_dedup_adjacent")
+
+
+def dedup_tensor_pair_(ids: Tensor, distances: Tensor):
+    """kernels.py:383-397.  Assumes sorted tensors!"""
+    (batch_size, queue_size) = ids.size()
+    (batch_size2, queue_size2) = distances.size()
+    assert batch_size == batch_size2
+    assert queue_size == queue_size2
+    assert ids.is_contiguous()
+    assert distances.is_contiguous()
+    _lib.require_cuda(ids, distances)
+    check(lib().vl_dedup_adjacent(ptr(ids), ptr(distances), ctypes.c_int64(batch_size), queue_size,
+                                  stream_of(ids)), "vl_dedup_adjacent")
+
+
+def punchout_duplicates_(ids: Tensor, distances: Tensor):
+    """kernels.py:400-406: dedup the sorted pair in place, then move the punched entries last;
+    returns the re-sorted (ids, distances)."""
+    dedup_tensor_pair_(ids, distances)
+    ids = ids.clone()
+    distances = distances.clone()
+    (batch_size, queue_size) = ids.size()
+    check(lib().vl_sort_pairs(ptr(ids), ptr(distances), ctypes.c_int64(batch_size), queue_size, 0,
+                              stream_of(ids)), "vl_sort_pairs")
+    assert ids.dtype == torch.int32
+    assert distances.dtype == torch.float32
+    return (ids, distances)
+
+
+def prune_(beams: Tensor, distances: Tensor, out_cols: Optional[int] = None, punch: bool = True):
+    """kernels.py:441-468: remove detourable links (x->z when d_xz > d_xy and d_xz > d_yz, z the
+    first neighbour of y), then order every row by distance.  Returns new (beams, distances);
+    `out_cols` (added) keeps only the first columns."""
+    assert beams.dtype == torch.int32
+    assert distances.dtype == torch.float32
+    assert beams.is_contiguous() and distances.is_contiguous()
+    _lib.require_cuda(beams, distances)
+    (batch_size, beam_size) = beams.size()
+    cols = beam_size if out_cols is None else out_cols
+    out_b = torch.empty((batch_size, cols), dtype=torch.int32, device=beams.device)
+    out_d = torch.empty((batch_size, cols), dtype=torch.float32, device=beams.device)
+    check(lib().vl_prune(ptr(beams), ptr(distances), ctypes.c_int64(batch_size), beam_size, 1 if punch else 0,
+                         ptr(out_b), ptr(out_d), cols, ptr(_lib.status_word(beams.device)), stream_of(beams)),
+          "vl_prune")
+    return (out_b, out_d)
+
+
+def punchout_excluded_(indices: Tensor, distances: Tensor, exclusions: Tensor):
+    """kernels.py:491-501: in place on (possibly column-sliced) views."""
+    (batch_size, queue_size) = indices.size()
+    (batch_size2, exclusion_size) = exclusions.size()
+    assert batch_size == batch_size2
+    assert indices.dtype == torch.int32 and distances.dtype == torch.float32
+    assert exclusions.dtype == torch.int32 and exclusions.is_contiguous()
+    assert indices.stride(1) == 1 and distances.stride(1) == 1
+    _lib.require_cuda(indices, distances, exclusions)
+    check(lib().vl_punchout_excluded(ptr(indices), ptr(distances), ctypes.c_int64(indices.stride(0)),
+                                     ctypes.c_int64(distances.stride(0)), ctypes.c_int64(batch_size), queue_size,
+                                     ptr(exclusions), exclusion_size, stream_of(indices)), "vl_punchout_excluded")
+
+
+def sort_pairs_(ids: Tensor, distances: Tensor, dedup: bool):
+    """Rows ordered by (distance, id) in place; with `dedup` also queue_sort's punch-and-compact."""
+    assert ids.is_contiguous() and distances.is_contiguous()
+    assert ids.dtype == torch.int32 and distances.dtype == torch.float32
+    _lib.require_cuda(ids, distances)
+    (batch_size, queue_size) = ids.size()
+    check(lib().vl_sort_pairs(ptr(ids), ptr(distances), ctypes.c_int64(batch_size), queue_size, 1 if dedup else 0,
+                              stream_of(ids)), "vl_sort_pairs")
+
+
+def index_by_tensor(a: Tensor, b: Tensor):
+    """kernels.py:554-559: row-wise gather a[i, b[i, j]]."""
+    return torch.gather(a, 1, b.long())
