@@ -1,0 +1,380 @@
+"""Benchmark of the ANN graph build / beam search hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
+
+One "step" is one complete graph build (`ANN(vectors=...)`: circulant start graph, up to
+`optimization_loops` rounds of fused beam search + prune + self-recall check) over the
+workload's synthetic vectors.  The JSON line reports build vectors/s (`value`, inputs already
+in HBM; `e2e` with host buffers), the search QPS and recall@10 of the built graph, the
+roofline of the dominant kernel, and a CPU baseline (the C oracle on a bounded sample).
+`--impl reference` times the reference's algorithm on the host cores only (the C oracle, all
+threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "vectorlink-gpu_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np
+import torch
+
+# workload shapes follow BASELINE.json's configs; all data is synthetic with seed 0.
+WORKLOADS = {
+    # config 1: 2,000 x 64 unit vectors, cosine, degree 16, beam 32
+    "c1": dict(n=2_000, dim=64, metric="cosine", degree=16, beam=32, queries=100, kind="gauss_unit"),
+    # config 2: 1,000,000 x 128 SIFT-like integer mixture, L2, degree 32, beam 64, 10,000 queries
+    "c2": dict(n=1_000_000, dim=128, metric="l2", degree=32, beam=64, queries=10_000, kind="sift_like", centres=256),
+    # config 3: 1,000,000 x 768 unit-norm embedding-like mixture, cosine, degree 64, beam 128
+    "c3": dict(n=1_000_000, dim=768, metric="cosine", degree=64, beam=128, queries=10_000, kind="embed_like",
+               centres=1000, noise=0.1),
+    # config 4 (per-GPU shard of it at N GPUs): 10,000,000 x 96 Deep-like, cosine, degree 32
+    "c4": dict(n=10_000_000, dim=96, metric="cosine", degree=32, beam=64, queries=10_000, kind="embed_like",
+               centres=4096, noise=0.3),
+}
+
+
+def ann_kwargs(w):
+    """Parameter mapping: beam_size = degree; recall_search_queue_factor = visit_queue_factor =
+    beam / degree; every other ANN keyword at its default.  search_seed_factor widens the
+    seed scan so that a seed lands in the query's cluster (the data has separated clusters)."""
+    f = max(1, w["beam"] // w["degree"])
+    kw = dict(beam_size=w["degree"], visit_queue_factor=f, recall_search_queue_factor=f, metric=w["metric"])
+    if w["kind"] != "gauss_unit":
+        kw["search_seed_factor"] = 30
+    return kw
+
+
+def make_data(w, n, device, seed=0, queries=None):
+    """Generator order: centres -> assignments -> noise -> queries (one torch generator)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    dim = w["dim"]
+    nq = w["queries"] if queries is None else queries
+
+    def draw(count):
+        if w["kind"] == "gauss_unit":
+            x = torch.randn((count, dim), device=device, generator=g)
+            return torch.nn.functional.normalize(x, dim=1)
+        out = torch.empty((count, dim), device=device)
+        for lo in range(0, count, 1_000_000):
+            hi = min(count, lo + 1_000_000)
+            assign = torch.randint(0, centres.size(0), (hi - lo,), device=device, generator=g)
+            noise = torch.randn((hi - lo, dim), device=device, generator=g)
+            if w["kind"] == "sift_like":
+                out[lo:hi] = (centres[assign] + 20.0 * noise).round().clamp(0, 255)
+            else:
+                out[lo:hi] = torch.nn.functional.normalize(centres[assign] + w["noise"] * noise, dim=1)
+        return out
+
+    centres = None
+    if w["kind"] == "sift_like":
+        centres = torch.rand((w["centres"], dim), device=device, generator=g) * 255.0
+    elif w["kind"] == "embed_like":
+        centres = torch.nn.functional.normalize(torch.randn((w["centres"], dim), device=device, generator=g), dim=1)
+    vectors = draw(n)
+    q = draw(nq)
+    return vectors.contiguous(), q.contiguous()
+
+
+def brute_force_topk(vectors, queries, k, metric):
+    """Exact top-k on the GPU in fp32 (ground truth for recall; measurement harness only)."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.set_float32_matmul_precision("highest")
+    best_d = torch.full((queries.size(0), k), float("inf"), device=vectors.device)
+    best_i = torch.zeros((queries.size(0), k), dtype=torch.int64, device=vectors.device)
+    qn = (queries * queries).sum(1, keepdim=True)
+    for lo in range(0, vectors.size(0), 262_144):
+        blk = vectors[lo:lo + 262_144]
+        dots = queries @ blk.t()
+        d = (qn - 2 * dots + (blk * blk).sum(1).unsqueeze(0)) if metric == "l2" else (1 - dots) / 2
+        cd, ci = torch.topk(d, min(k, blk.size(0)), dim=1, largest=False)
+        alld = torch.cat([best_d, cd], 1)
+        alli = torch.cat([best_i, ci + lo], 1)
+        best_d, sel = torch.topk(alld, k, dim=1, largest=False)
+        best_i = torch.gather(alli, 1, sel)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    return best_i
+
+
+def recall_at_k(found_ids, truth, k):
+    f = found_ids[:, :k].long()
+    hits = (f.unsqueeze(2) == truth[:, :k].unsqueeze(1)).any(2).sum().item()
+    return hits / (truth.size(0) * k)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 9 for i in range(4) if r[5 + i] == "Active"})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def oracle_build_rate(w, sample_n, seed=0):
+    """The C oracle (all host threads) building the graph of a `sample_n`-vector draw of the
+    workload with the same ANN parameters; returns (vectors/s, seconds, loops, threads)."""
+    import oracle
+    vec, _ = make_data(w, sample_n, "cpu", seed, queries=1)
+    kw = ann_kwargs(w)
+    metric = kw.pop("metric")
+    kw.pop("search_seed_factor", None)
+    cfg = oracle.make_config(**kw)
+    t0 = time.time()
+    _, _, loops, _ = oracle.generate_ann(vec.numpy(), cfg, metric=metric)
+    dt = time.time() - t0
+    return sample_n / dt, dt, loops, oracle.num_threads()
+
+
+def run_reference(args, w, name):
+    """The reference's CPU implementation of the path (the C restatement; the Numba kernels
+    themselves simulate at about one CUDA block per second) on a bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = args.sample or max(500, min(w["n"], int(2_000_000 / (w["dim"] * (w["degree"] / 16)))))
+    rates = []
+    for _ in range(args.warmup):
+        oracle_build_rate(w, min(sample, 500))
+    t_all = time.time()
+    for _ in range(args.steps):
+        rate, dt, loops, threads = oracle_build_rate(w, sample)
+        rates.append(rate)
+    ms = (time.time() - t_all) / max(1, args.steps) * 1e3
+    value = float(np.mean(rates))
+    line = {"impl": "reference", "metric": "graph_build_vectors_per_s", "value": value, "unit": "vectors/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "sample_vectors": sample, **{k: v for k, v in ann_kwargs(w).items()}},
+            "cpu_baseline": {"value": value, "unit": "vectors/s", "cores": threads, "kind": "port",
+                             "sample": f"full build of a {sample}-vector draw of {name} ({loops} loops), C oracle with OpenMP"},
+            "e2e": {"value": value, "unit": "vectors/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--n", type=int, default=0, help="override the vector count (per GPU)")
+    ap.add_argument("--sample", type=int, default=0, help="vectors in the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--loops", type=int, default=0, help="override optimization_loops")
+    args = ap.parse_args()
+    name = args.workload
+    w = dict(WORKLOADS[name])
+    if args.n:
+        w["n"] = args.n
+    if args.impl == "reference":
+        run_reference(args, w, name)
+        return
+
+    import torch.distributed as dist
+    from vectorlink_gpu import ANN, _lib
+    from vectorlink_gpu import ann as vl_ann
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    kw = ann_kwargs(w)
+    if args.loops:
+        kw["optimization_loops"] = args.loops
+    # weak scaling: every rank owns its own shard of w["n"] vectors (different seed per rank);
+    # shards are independent in the build, so there is no data-path collective in a step
+    vectors, queries = make_data(w, w["n"], dev, seed=rank)
+    n, dim = vectors.shape
+    host_vectors = torch.empty((n, dim), dtype=torch.float32, pin_memory=True)
+    host_vectors.copy_(vectors)
+    host_beams = torch.empty((n, kw["beam_size"]), dtype=torch.int32, pin_memory=True)
+    host_dist = torch.empty((n, kw["beam_size"]), dtype=torch.float32, pin_memory=True)
+
+    def step_device():
+        return ANN(vectors=vectors, **kw)
+
+    def step_e2e():
+        v = host_vectors.to(dev, non_blocking=True)
+        a = ANN(vectors=v, **kw)
+        host_beams.copy_(a.beams, non_blocking=True)
+        host_dist.copy_(a.distances, non_blocking=True)
+        torch.cuda.synchronize(dev)
+        return a
+
+    for _ in range(args.warmup):
+        ann = step_device()
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    vl_ann.PROFILE = []
+    launches0 = _lib.LAUNCHES
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        ann = step_device()
+    ev1.record()
+    barrier()
+    launches = _lib.LAUNCHES - launches0
+    profile = vl_ann.PROFILE
+    vl_ann.PROFILE = None
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # the dominant kernel: the fused beam search over all rows (one launch per build round)
+    k_ms = [p["start"].elapsed_time(p["end"]) for p in profile]
+    k_evals = [p["evals"] for p in profile]
+    big = [i for i, p in enumerate(profile) if p["rows"] == n]
+    bytes_per_eval = 4 * dim + 12
+    if big:
+        ach = sum(k_evals[i] for i in big) * bytes_per_eval / (sum(k_ms[i] for i in big) * 1e-3) / 1e9
+        kernel_share = sum(k_ms) / ms_total
+    else:
+        ach, kernel_share = 0.0, 0.0
+
+    # end to end with host buffers
+    step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    # search over the built graph
+    sq = ann.search(queries)
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(3, args.steps)
+    vl_ann.PROFILE = []
+    s0.record()
+    for _ in range(reps):
+        sq = ann.search(queries)
+    s1.record()
+    barrier()
+    sprof = vl_ann.PROFILE
+    vl_ann.PROFILE = None
+    search_ms = s0.elapsed_time(s1) / reps
+    s_k_ms = sum(p["start"].elapsed_time(p["end"]) for p in sprof) / reps
+    s_evals = sum(p["evals"] for p in sprof) / reps
+    truth = brute_force_topk(vectors, queries, 10, w["metric"])
+    recall = recall_at_k(sq.indices, truth, 10)
+    gsample = min(n, 10_000)
+    gtruth = brute_force_topk(vectors, vectors[:gsample], 11, w["metric"])[:, 1:]
+    graph_recall = recall_at_k(ann.beams[:gsample], gtruth, 10)
+    status = _lib.read_status(dev)
+
+    times = torch.tensor([ms_total, e2e_ms, search_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, search_ms = [float(x) for x in times.tolist()]
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650"
+        ms_per_step = ms_total / args.steps
+        line = {
+            "metric": "graph_build_vectors_per_s", "value": world * n / (ms_per_step * 1e-3), "unit": "vectors/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "vectors_per_gpu": n, "dim": dim, **kw, "loops_run": vl_ann.generate_ann.last_loops,
+                       "l2_policy": "inputs (vectors %d MB + graph) exceed the 126 MB L2" % (n * dim * 4 // 2**20),
+                       "sharding": "one independent shard per GPU, no collective in the build step" if world > 1 else "none"},
+            "e2e": {"value": world * n / (e2e_ms / args.steps * 1e-3), "unit": "vectors/s",
+                    "h2d_bytes_per_step": n * dim * 4, "d2h_bytes_per_step": n * kw["beam_size"] * 8},
+            "gpu_launches": launches,
+            "search": {"qps": world * queries.size(0) / (search_ms * 1e-3), "queries": queries.size(0), "k": 10,
+                       "recall_at_10": recall, "ms": search_ms,
+                       "kernel_gbs": (s_evals * bytes_per_eval / (s_k_ms * 1e-3) / 1e9) if s_k_ms else None},
+            "graph_recall_at_10": graph_recall,
+            "roofline": {"bound": "hbm", "kernel": "beam_search_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
+                         "frac": ach / peak, "peak_source": peak_kind, "frac_of_8TBs_nominal": ach / 8000.0,
+                         "bytes_per_eval": bytes_per_eval, "evals_per_launch": k_evals[big[0]] if big else 0,
+                         "launch_ms": (sum(k_ms[i] for i in big) / len(big)) if big else None,
+                         "kernel_share_of_step": kernel_share, "traffic": None},
+            "clocks": clocks, "status_word": status,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            sample = args.sample or max(500, min(n, int(2_000_000 / (dim * (kw["beam_size"] / 16)))))
+            rate, dt, loops, threads = oracle_build_rate(w, sample)
+            line["cpu_baseline"] = {"value": rate, "unit": "vectors/s", "cores": threads, "kind": "port",
+                                    "sample": f"full build of a {sample}-vector draw of {name} ({loops} loops, {dt:.1f} s), "
+                                              "C oracle with OpenMP"}
+        traffic_file = os.path.join(ROOT, "profiles", "beam_search_traffic.json")
+        if os.path.exists(traffic_file):
+            try:
+                tr = json.load(open(traffic_file))
+                if big and tr.get("dram_bytes_per_eval"):
+                    line["roofline"]["traffic"] = tr["dram_bytes_per_eval"] * k_evals[big[0]]
+                    line["roofline"]["traffic_note"] = tr.get("note")
+            except Exception:
+                pass
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -105,6 +105,18 @@ def primes_table(count: int = 965) -> np.ndarray:
     return table[:count]
 
 
+def seed_offsets(count: int) -> np.ndarray:
+    """The seed table, continued past its 965 entries for widened seed scans (not in the
+    reference): entry j = table[j mod 965] * (j div 965 + 1) + j, kept below 2^30."""
+    table = primes_table().astype(np.int64)
+    if count <= 965:
+        return table[:count].astype(np.int32)
+    j = np.arange(count, dtype=np.int64)
+    ext = (table[j % 965] * (j // 965 + 1) + j) % (1 << 30)
+    ext[:965] = table
+    return ext.astype(np.int32)
+
+
 def pair_distance(a, b, metric=COSINE) -> float:
     a, b = _f32(a), _f32(b)
     return float(lib().vlo_pair_distance(_p(a, _F), _p(b, _F), ctypes.c_int(a.shape[0]),
@@ -262,12 +274,17 @@ def initial_search_queue(vectors, queries, config: dict, metric=COSINE) -> Queue
     extra = max(q, config["parallel_visit_count"] * config["beam_size"])
     b = queries.shape[0]
     queue = Queue(b, q, q + extra)
-    seeds = circulants(b, vectors.shape[0], primes_table(q))
+    count = q * max(1, int(config.get("search_seed_factor", 1)))
+    seeds = circulants(b, vectors.shape[0], seed_offsets(count))
     # distances of query b against the seed rows: search_from_seeds over a one-column "graph"
-    d = np.empty((b, q), dtype=np.float32)
     ident = np.arange(vectors.shape[0], dtype=np.int32).reshape(-1, 1)
     _, d = search_from_seeds(queries, seeds, ident, vectors, metric)
-    queue.insert(seeds, d)
+    # piecewise inserts == the best q distinct (distance, id) pairs of all seeds
+    for c in range(0, count, extra):
+        queue.insert(seeds[:, c:c + extra], d[:, c:c + extra])
+    if count > extra:   # a widened scan hands over only its best q; the columns behind start empty
+        queue.indices[:, q:] = MAXINT
+        queue.distances[:, q:] = MAXFLOAT
     return queue
 
 

@@ -218,8 +218,12 @@ def test_graph_and_search_recall_against_brute_force(built_lib):
     centres = rng.uniform(0, 255, (64, dim))
     vectors = np.round(centres[rng.integers(0, 64, nvec)] + rng.normal(0, 20, (nvec, dim))).clip(0, 255).astype(np.float32)
     queries = np.round(centres[rng.integers(0, 64, 200)] + rng.normal(0, 20, (200, dim))).clip(0, 255).astype(np.float32)
-    ann = ANN(t(vectors), beam_size=32, visit_queue_factor=2, recall_search_queue_factor=2, metric="l2")
+    kw = dict(beam_size=32, visit_queue_factor=2, recall_search_queue_factor=2, search_seed_factor=20)
+    ann = ANN(t(vectors), metric="l2", **kw)
     sq = ann.search(t(queries))
+    # the widened seed scan is the oracle's too, bit for bit
+    osq = oracle.search(vectors, n(ann.beams), queries, oracle.make_config(**kw), metric="l2")
+    assert np.array_equal(n(sq.indices), osq.indices) and np.array_equal(n(sq.distances), osq.distances)
     truth = oracle.bruteforce_knn(vectors, queries, 10, metric="l2")
     got = n(sq.indices[:, :10])
     recall = np.mean([len(set(got[i]) & set(truth[i])) / 10 for i in range(200)])

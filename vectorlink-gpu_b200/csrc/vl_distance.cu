@@ -42,7 +42,13 @@ gather_distance_kernel(const float* __restrict__ vectors, int64_t n, int dim,
         float4 qr[JP];
         vl_load_query<LPR, JP, ALIGNED>(q, dim, lg, qr);
         int32_t node = 0;
-        if (visit) node = __ldg(visit + r * segs + s);
+        if (visit) {
+            node = __ldg(visit + r * segs + s);
+            if (node != VL_MAXINT && (node < 0 || (int64_t)node >= n)) {
+                if (lane == 0) atomicOr(status, VL_STATUS_BAD_ID);
+                node = VL_MAXINT;
+            }
+        }
         const int64_t out0 = r * (int64_t)segs * seg_len + (int64_t)s * seg_len;
         for (int m0 = 0; m0 < seg_len; m0 += G) {
             const int m = m0 + g;
@@ -97,8 +103,9 @@ extern "C" int vl_calculate_distances(const float* vectors, int64_t n, int dim, 
                                       int64_t rows, const int32_t* ids, int w, float* dist_out, int metric,
                                       int* status, void* stream)
 {
+    VL_CHECK_ARG(dim > 0 && w >= 0 && rows >= 0 && n >= 0, "vl_calculate_distances: bad size");
+    if (rows == 0 || w == 0) return 0;
     VL_CHECK_ARG(vectors && queries && ids && dist_out && status, "vl_calculate_distances: null pointer");
-    VL_CHECK_ARG(dim > 0 && w >= 0 && rows >= 0 && n > 0, "vl_calculate_distances: bad size");
     VL_CHECK_ARG(metric == VL_METRIC_COSINE || metric == VL_METRIC_SQL2, "vl_calculate_distances: unknown metric %d", metric);
     cudaStream_t st = (cudaStream_t)stream;
     if (metric == VL_METRIC_COSINE)
@@ -110,8 +117,9 @@ extern "C" int vl_search_from_seeds(const float* queries, int64_t b, const int32
                                     const int32_t* graph, int w, const float* vectors, int64_t n, int dim,
                                     int32_t* idx_out, float* dist_out, int metric, int* status, void* stream)
 {
+    VL_CHECK_ARG(dim > 0 && w >= 0 && v >= 0 && b >= 0 && n >= 0, "vl_search_from_seeds: bad size");
+    if (b == 0 || v == 0 || w == 0) return 0;
     VL_CHECK_ARG(vectors && queries && visit && graph && idx_out && dist_out && status, "vl_search_from_seeds: null pointer");
-    VL_CHECK_ARG(dim > 0 && w >= 0 && v >= 0 && b >= 0 && n > 0, "vl_search_from_seeds: bad size");
     VL_CHECK_ARG(metric == VL_METRIC_COSINE || metric == VL_METRIC_SQL2, "vl_search_from_seeds: unknown metric %d", metric);
     cudaStream_t st = (cudaStream_t)stream;
     if (metric == VL_METRIC_COSINE)

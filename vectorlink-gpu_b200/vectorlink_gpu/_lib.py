@@ -45,6 +45,7 @@ class BeamParams(ctypes.Structure):
 
 
 _lib = None
+LAUNCHES = 0   # kernels of this library launched so far (kept by the Python wrappers)
 
 
 class VlError(RuntimeError):
@@ -78,9 +79,14 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+KERNELS_PER_CALL = {"vl_dedup_adjacent": 2, "vl_seen_add": 3}   # every other entry point launches one
+
+
 def check(rc: int, what: str) -> None:
+    global LAUNCHES
     if rc != 0:
         raise VlError(f"{what} failed ({rc}): {lib().vl_last_error().decode()}")
+    LAUNCHES += KERNELS_PER_CALL.get(what, 1)
 
 
 def ptr(t):
@@ -103,9 +109,16 @@ def require_cuda(*tensors) -> None:
 _status = {}
 
 
+def _device_key(device) -> torch.device:
+    d = torch.device(device)
+    if d.type == "cuda" and d.index is None:
+        d = torch.device("cuda", torch.cuda.current_device())
+    return d
+
+
 def status_word(device) -> torch.Tensor:
     """One int32 per device that kernels OR VL_STATUS_* bits into."""
-    key = torch.device(device)
+    key = _device_key(device)
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
     return _status[key]

@@ -18,7 +18,7 @@ from torch import Tensor
 
 from . import _lib
 from ._lib import BeamParams, check, lib, ptr, stream_of
-from .constants import MAXFLOAT, MAXINT
+from .constants import MAXFLOAT, MAXINT, PRIMES_HOST
 from .kernels import calculate_distances, metric_code, prune_, search_from_seeds, sort_pairs_
 from .log import log_time
 from . import log as _log
@@ -26,6 +26,9 @@ from .queue import Queue
 from .utils import add_new_to_seen_, generate_circulant_beams, generate_queue_circulants, primes
 
 FUSED_MAX_SMEM_PER_ROW = 200 * 1024
+# When set to a list, every fused-kernel launch appends its CUDA events (recorded on the
+# launching stream) and its count of distance evaluations: the benchmark's roofline figures.
+PROFILE = None
 
 
 def _metric_of(config: Dict):
@@ -96,7 +99,16 @@ def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len
     p.n_checks = flags.size(1)
     p.group_full = full.data_ptr()
     p.status = _lib.status_word(vectors.device).data_ptr()
+    if PROFILE is not None:
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
     check(lib().vl_beam_search(ctypes.byref(p), stream_of(vectors)), "vl_beam_search")
+    if PROFILE is not None:
+        end.record()
+        k_none = (p.seen_cap + pvc - 1) // pvc + 1
+        PROFILE.append({"start": start, "end": end, "rows": int(p.rows), "graph_w": int(p.graph_w),
+                        "iterations": int(min(n_iters, k_none)), "evals": int(p.rows) * min(n_iters, k_none) * pvc * int(p.graph_w)})
 
 
 def _natural_end(flag_row: List[int], config: Dict) -> int:
@@ -325,16 +337,27 @@ def query_distances(query_vectors: Tensor, vectors: Tensor, ids: Tensor, metric=
 
 
 def initial_search_queue(vectors: Tensor, query_vectors: Tensor, config: Dict):
-    """ann.py:217-232: circulant seeds (b + p_j) mod N for query row b."""
+    """ann.py:217-232: circulant seeds (b + p_j) mod N for query row b; the queue starts as the
+    Q = recall_search_queue_factor * beam_size seeds ordered by distance.
+    config["search_seed_factor"] (added, default 1 = the reference) scans that many times Q
+    seeds and keeps the best Q: on data with well separated clusters the graph has no links
+    between clusters, so a search only finds a query's neighbourhood if a seed lands in it."""
     queue_size = config["recall_search_queue_factor"] * config["beam_size"]
     (batch_size, _) = query_vectors.size()
     extra_capacity = max(queue_size, config["parallel_visit_count"] * config["beam_size"])
     queue = Queue(batch_size, queue_size, queue_size + extra_capacity, device=vectors.device)
-    p = primes(queue_size, vectors.device)
+    seed_count = queue_size * max(1, int(config.get("search_seed_factor", 1)))
+    p = primes(seed_count, vectors.device)
     (vector_count, _) = vectors.size()
     initial_queue_indices = generate_queue_circulants(batch_size, vector_count, p)
     d = query_distances(query_vectors, vectors, initial_queue_indices, _metric_of(config))
-    queue.insert(initial_queue_indices, d)
+    if seed_count <= extra_capacity:
+        queue.insert(initial_queue_indices, d)
+    else:
+        # same result as inserting the seeds piecewise: the best Q distinct (distance, id) pairs
+        sort_pairs_(initial_queue_indices, d, dedup=True)
+        queue.indices.narrow(1, 0, queue_size).copy_(initial_queue_indices.narrow(1, 0, queue_size))
+        queue.distances.narrow(1, 0, queue_size).copy_(d.narrow(1, 0, queue_size))
     return queue
 
 
@@ -372,13 +395,15 @@ def print_timestamp(msg):
 class ANN:
     """ann.py:356-489.  `ANN(vectors=...)` builds the graph; `.beams` int32 [N, beam_size],
     `.distances` fp32 [N, beam_size], `.search(query)` returns the search `Queue`.
-    Added keyword: metric ("cosine" - the reference's distance on unit vectors - or "l2")."""
+    Added keywords: metric ("cosine" - the reference's distance on unit vectors - or "l2") and
+    search_seed_factor (how many times Q seeds `.search` scans for its starting queue; 1 = the
+    reference)."""
 
     def __init__(self, vectors: Tensor, prune: bool = True, beam_size: int = 24, parallel_visit_count: int = 4,
                  beam_queue_factor: int = 3, visit_queue_factor: int = 3, exclude_factor: int = 5,
                  optimization_loops: int = 3, batch_size: int = 10_000, recall_search_queue_factor: int = 3,
                  speculative_readahead: int = 5, beams: Optional[Tensor] = None, distances: Optional[Tensor] = None,
-                 metric: str = "cosine"):
+                 metric: str = "cosine", search_seed_factor: int = 1):
         (count, dim) = vectors.size()
         assert vectors.dtype == torch.float32
         _lib.require_cuda(vectors)
@@ -397,6 +422,8 @@ class ANN:
         }
         if metric != "cosine":
             self.configuration["metric"] = metric
+        if search_seed_factor != 1:
+            self.configuration["search_seed_factor"] = search_seed_factor
         self.vectors = vectors.contiguous()
         wall_start = time.time()
         if beams is not None:

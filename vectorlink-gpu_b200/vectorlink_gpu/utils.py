@@ -20,8 +20,16 @@ def generate_random_vectors(number_of_vectors: int, dimensions: int = 1536, devi
 
 
 def primes(size: int, device="cuda") -> Tensor:
-    """utils.py:22-23: the first `size` entries of the seed table."""
-    return primes_on(device).narrow(0, 0, size)
+    """utils.py:22-23: the first `size` entries of the seed table.  Past the table's 965
+    entries (which no reference configuration reaches) further offsets are derived from it:
+    entry j is table[j mod 965] * (j div 965 + 1) + j, kept below 2^30."""
+    table = primes_on(device)
+    if size <= table.numel():
+        return table.narrow(0, 0, size)
+    j = torch.arange(size, device=table.device, dtype=torch.int64)
+    ext = (table.long()[j % table.numel()] * (j // table.numel() + 1) + j) % (1 << 30)
+    ext[: table.numel()] = table.long()
+    return ext.to(torch.int32)
 
 
 def generate_queue_circulants(batch_size: int, num_vecs: int, primes: Tensor) -> Tensor:
