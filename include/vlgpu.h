@@ -89,6 +89,17 @@ int vl_dedup_sort_ids(int32_t* ids, int64_t b, int e, void* stream);
 int vl_seen_add(int32_t* seen, int64_t b, int e, const int32_t* visit, int v, int* scratch, int* first_out,
                 void* stream);
 
+/* No counterpart in the reference: vl_seen_add for callers that cannot provide (or allocate)
+ * the scratch buffer - a process whose framework reserved all device memory up front, a plugin
+ * that may not allocate after start-up, a loop that must never reach cudaMalloc.  The column
+ * flags live in a fixed 16 KB device array inside the library (one per GPU, held until exit),
+ * so e <= VL_SEEN_NOALLOC_MAX_WIDTH; wider lists are rejected with an error.  Calls nothing
+ * that allocates.  Same results as vl_seen_add.  All calls on a GPU share the array: calls
+ * that overlap on the GPU race, keep them stream-ordered.  The first call on a device looks up
+ * the array's address and should happen before any stream capture begins. */
+#define VL_SEEN_NOALLOC_MAX_WIDTH 4096
+int vl_seen_add_noalloc(int32_t* seen, int64_t b, int e, const int32_t* visit, int v, int* first_out, void* stream);
+
 /* prune_ (kernels.py:441-468, kernel 409-438) followed by the cut to the first out_cols
  * columns (ann.py:190-193): rows of beams/dist [n, w], sorted by distance on entry, lose the
  * links x->z that have a detour over y's first neighbour (do_punch != 0), are ordered by

@@ -339,3 +339,81 @@ extern "C" int vl_seen_add(int32_t* seen, int64_t b, int e, const int32_t* visit
     VL_CHECK_LAUNCH("dedup_sort_ids_kernel");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// vl_seen_add_noalloc: the visited-list update of vl_seen_add for callers that cannot give it
+// scratch memory.  Some hosts of this library own no allocator at the point of the call: a
+// serving process whose framework reserved all of HBM up front and hands out nothing later, a
+// plugin that is forbidden to allocate after initialisation, or a latency-critical loop in
+// which cudaMalloc (which synchronises the whole device) must never run.  For them the per-
+// column "is this column used" flags live in the fixed array below instead of a caller buffer.
+//
+// The array is file-scope device memory: every GPU that loads this library holds one copy of
+// it (16 KB) until the process exits.  Its name is a host-side handle, not a device address,
+// so host code must not pass it to a kernel; the address is taken once per device with
+// cudaGetSymbolAddress while that device is current, and that pointer is what the kernels get.
+// All calls on a device share the array and it keeps whatever the previous call left, so each
+// call first clears the part it uses; two calls that overlap on the GPU (different streams)
+// would race on it - keep calls on one stream or otherwise ordered.
+// The first call on a device performs the address look-up; make that first call outside of
+// any stream capture.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+// VL_SEEN_NOALLOC_MAX_WIDTH (vlgpu.h): most columns (`e`) the fixed scratch can serve
+static __device__ __align__(256) int g_seen_scratch[VL_SEEN_NOALLOC_MAX_WIDTH];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+int* g_scratch_addr[kMaxDevices] = {nullptr};
+
+// Device address of g_seen_scratch on the current device (looked up once per device).
+int seen_scratch_address(int** out)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    VL_CHECK_ARG(e == cudaSuccess, "vl_seen_add_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    VL_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "vl_seen_add_noalloc: device %d outside 0..%d", dev, kMaxDevices - 1);
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_addr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_seen_scratch);
+        VL_CHECK_ARG(e == cudaSuccess && p, "vl_seen_add_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_scratch_addr[dev] = static_cast<int*>(p);
+    }
+    *out = g_scratch_addr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int vl_seen_add_noalloc(int32_t* seen, int64_t b, int e, const int32_t* visit, int v, int* first_out,
+                                   void* stream)
+{
+    VL_CHECK_ARG(seen && visit && first_out, "vl_seen_add_noalloc: null pointer");
+    VL_CHECK_ARG(e >= 0 && e <= VL_SEEN_NOALLOC_MAX_WIDTH,
+                 "vl_seen_add_noalloc: list width %d exceeds the fixed scratch of %d columns; use vl_seen_add with a "
+                 "caller-provided scratch buffer", e, VL_SEEN_NOALLOC_MAX_WIDTH);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (e == 0 || b == 0) {
+        int minus = -1;
+        cudaMemcpyAsync(first_out, &minus, sizeof(int), cudaMemcpyHostToDevice, st);
+        return 0;
+    }
+    int* scratch = nullptr;
+    int rc = seen_scratch_address(&scratch);
+    if (rc) return rc;
+    // the array still holds the previous call's flags: clear the e entries this call reads
+    cudaError_t ce = cudaMemsetAsync(scratch, 0, sizeof(int) * e, st);
+    VL_CHECK_ARG(ce == cudaSuccess, "vl_seen_add_noalloc: cudaMemsetAsync: %s", cudaGetErrorString(ce));
+    column_used_kernel<<<blocks_for(b * e, 256), 256, 0, st>>>(seen, b * e, e, scratch);
+    VL_CHECK_LAUNCH("column_used_kernel");
+    first_free_column_kernel<<<1, 256, 0, st>>>(scratch, e, first_out);
+    VL_CHECK_LAUNCH("first_free_column_kernel");
+    int p = pow2_at_least(e);
+    dedup_sort_ids_kernel<<<(unsigned)b, kSortThreads, sizeof(vl_key_t) * p, st>>>(seen, e, p, visit, v, first_out);
+    VL_CHECK_LAUNCH("dedup_sort_ids_kernel");
+    return 0;
+}
