@@ -152,7 +152,8 @@ __device__ __forceinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int 
     return true;
 }
 
-template <int LPR, int JP, int METRIC>
+// JU > 0: exact-fit rows (dim == 4*LPR*JU, see vl_load_exact); JU == 0: any dim % 4 == 0.
+template <int LPR, int JP, int JU, int METRIC>
 __global__ void __launch_bounds__(kBeamWarps * 32)
 beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 {
@@ -183,8 +184,10 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         vl_key_t* vq = reinterpret_cast<vl_key_t*>(base + lay.vq_a);
         vl_key_t* vq_n = reinterpret_cast<vl_key_t*>(base + lay.vq_b);
         const float* q = p.queries + row * (int64_t)p.dim;
-        float4 qr[JP];
-        vl_load_query<LPR, JP, true>(q, p.dim, lg, qr);
+        constexpr int JQ = JU > 0 ? JU : JP;
+        float4 qr[JQ];
+        if constexpr (JU > 0) vl_load_exact<LPR, JU>(q, lg, qr);
+        else vl_load_query<LPR, JP, true>(q, p.dim, lg, qr);
 
         // ---- prologue: Queue.insert of the seeds into an empty queue (queue.py:37-61) ----
         for (int i = lane; i < sq_len; i += 32) sq[i] = kSent;
@@ -223,18 +226,21 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 vl_key_t* t = vq; vq = vq_n; vq_n = t;
             }
             // ---- neighbour ids of the popped nodes (kernels.py:244) ----
-            for (int i = lane; i < m_total; i += 32) {
-                int v = i / wb, j = i - v * wb;
+            for (int v = 0; v < pvc; ++v) {
                 int32_t node = pop[v];
-                int32_t id = VL_MAXINT;
-                if (node != VL_MAXINT) {
-                    if (node < 0 || (int64_t)node >= p.n) atomicOr(p.status, VL_STATUS_BAD_ID);
-                    else {
-                        id = __ldg(p.graph + (int64_t)node * wb + j);
+                if (node != VL_MAXINT && (node < 0 || (int64_t)node >= p.n)) {
+                    if (lane == 0) atomicOr(p.status, VL_STATUS_BAD_ID);
+                    node = VL_MAXINT;
+                }
+                const int32_t* grow = p.graph + (int64_t)(node == VL_MAXINT ? 0 : node) * wb;
+                for (int j = lane; j < wb; j += 32) {
+                    int32_t id = VL_MAXINT;
+                    if (node != VL_MAXINT) {
+                        id = __ldg(grow + j);
                         if (id != VL_MAXINT && (id < 0 || (int64_t)id >= p.n)) { atomicOr(p.status, VL_STATUS_BAD_ID); id = VL_MAXINT; }
                     }
+                    cand[v * wb + j] = make_uint2((uint32_t)id, sent_ord);
                 }
-                cand[i] = make_uint2((uint32_t)id, sent_ord);
             }
             __syncwarp();
             // ---- gathered distances (kernels.py:248-257), two steps in flight ----
@@ -245,11 +251,20 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 const bool la = ida != VL_MAXINT, lb = idb != VL_MAXINT;
                 const float* ra = p.vectors + (int64_t)(la ? ida : 0) * p.dim;
                 const float* rb = p.vectors + (int64_t)(lb ? idb : 0) * p.dim;
-                float4 xa[JP], xb[JP];
-                vl_load_row<LPR, JP, true>(ra, p.dim, lg, la, xa);
-                vl_load_row<LPR, JP, true>(rb, p.dim, lg, lb, xb);
-                float da = vl_row_distance<LPR, JP, METRIC, true>(xa, qr, ra, q, p.dim, lg, la);
-                float db = vl_row_distance<LPR, JP, METRIC, true>(xb, qr, rb, q, p.dim, lg, lb);
+                float da, db;
+                if constexpr (JU > 0) {
+                    float4 xa[JU], xb[JU];
+                    vl_load_exact<LPR, JU>(ra, lg, xa);
+                    vl_load_exact<LPR, JU>(rb, lg, xb);
+                    da = vl_exact_distance<LPR, JP, JU, METRIC>(xa, qr);
+                    db = vl_exact_distance<LPR, JP, JU, METRIC>(xb, qr);
+                } else {
+                    float4 xa[JP], xb[JP];
+                    vl_load_row<LPR, JP, true>(ra, p.dim, lg, la, xa);
+                    vl_load_row<LPR, JP, true>(rb, p.dim, lg, lb, xb);
+                    da = vl_row_distance<LPR, JP, METRIC, true>(xa, qr, ra, q, p.dim, lg, la);
+                    db = vl_row_distance<LPR, JP, METRIC, true>(xb, qr, rb, q, p.dim, lg, lb);
+                }
                 if (lg == 0) {
                     if (la) cand[ma].y = vl_ord(da);
                     if (lb) cand[mb].y = vl_ord(db);
@@ -285,10 +300,11 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 break;
             }
             bool changed = false;
+            vl_key_t cut = sq[sq_len - 1];
             for (int c0 = 0; c0 < m_total; c0 += 32) {
                 const int c = c0 + lane;
                 vl_key_t key = c < m_total ? candk[c] : kSent;
-                bool want = key < sq[sq_len - 1];
+                bool want = key < cut;
                 if (!__any_sync(0xffffffffu, want)) continue;
                 if (want) {
                     int32_t id = vl_key_id(key);
@@ -302,6 +318,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 }
                 if (!__any_sync(0xffffffffu, want)) continue;
                 changed |= merge_chunk(sq, sq_n, sq_len, key, want, lane, mpos);
+                cut = sq[sq_len - 1];
             }
             if (changed && (k % p.readahead) == 0 && lane == 0) {
                 int chk = k / p.readahead - 1;
@@ -314,14 +331,16 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 if (lane < ncopy && mine != VL_MAXINT) hash_insert(hash, lay.hash_slots, lay.hash_shift, mine, p.status);
                 if (__any_sync(0xffffffffu, lane < ncopy && mine == VL_MAXINT)) always_full = false;
                 __syncwarp();
+                vl_key_t vcut = vq[vq_len - 1];
                 for (int c0 = 0; c0 < m_total; c0 += 32) {
                     const int c = c0 + lane;
                     vl_key_t key = c < m_total ? candk[c] : kSent;
-                    bool want = key < vq[vq_len - 1];
+                    bool want = key < vcut;
                     if (!__any_sync(0xffffffffu, want)) continue;
                     if (want && hash_contains(hash, lay.hash_slots, lay.hash_shift, vl_key_id(key))) want = false;
                     if (!__any_sync(0xffffffffu, want)) continue;
                     merge_chunk(vq, vq_n, vq_len, key, want, lane, mpos);
+                    vcut = vq[vq_len - 1];
                 }
             }
         }
@@ -340,10 +359,10 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 
 struct BeamPlan { BeamSmem lay; int warps; int blocks; size_t smem; };
 
-template <int LPR, int JP, int METRIC>
+template <int LPR, int JP, int JU, int METRIC>
 int plan_and_launch(const vl_beam_params& p, BeamPlan& plan, bool launch, cudaStream_t stream)
 {
-    auto kernel = beam_search_kernel<LPR, JP, METRIC>;
+    auto kernel = beam_search_kernel<LPR, JP, JU, METRIC>;
     plan.lay = beam_smem_layout(p.pvc * p.graph_w, p.sq_len, p.vq_len, p.seen_cap);
     int dev = 0, sms = 0, max_smem = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -393,9 +412,25 @@ int beam_dispatch(const vl_beam_params* pp, BeamPlan& plan, bool launch, cudaStr
     if (p.rows == 0) { plan.blocks = 0; plan.warps = kBeamWarps; plan.lay = beam_smem_layout(p.pvc * p.graph_w, p.sq_len, p.vq_len, p.seen_cap); return 0; }
     VlShape shape = vl_pick_shape(p.dim);
     int rc = 0;
+    const int chunks = p.dim / 4;
+    // exact-fit instantiations for the row sizes that matter (no per-chunk bounds tests)
+#define VL_EXACT(L, J, U)                                                                              \
+    if (shape.lpr == L && shape.jp == J && chunks == L * U) {                                          \
+        if (p.metric == VL_METRIC_COSINE) return plan_and_launch<L, J, U, VL_METRIC_COSINE>(p, plan, launch, stream); \
+        return plan_and_launch<L, J, U, VL_METRIC_SQL2>(p, plan, launch, stream);                      \
+    }
+    VL_EXACT(8, 2, 2)     // dim 64
+    VL_EXACT(8, 4, 3)     // dim 96
+    VL_EXACT(8, 4, 4)     // dim 128
+    VL_EXACT(16, 4, 4)    // dim 256
+    VL_EXACT(32, 4, 3)    // dim 384
+    VL_EXACT(32, 4, 4)    // dim 512
+    VL_EXACT(32, 8, 6)    // dim 768
+    VL_EXACT(32, 8, 8)    // dim 1024
+#undef VL_EXACT
     VL_DISPATCH_SHAPE(shape, {
-        if (p.metric == VL_METRIC_COSINE) rc = plan_and_launch<LPR, JP, VL_METRIC_COSINE>(p, plan, launch, stream);
-        else rc = plan_and_launch<LPR, JP, VL_METRIC_SQL2>(p, plan, launch, stream);
+        if (p.metric == VL_METRIC_COSINE) rc = plan_and_launch<LPR, JP, 0, VL_METRIC_COSINE>(p, plan, launch, stream);
+        else rc = plan_and_launch<LPR, JP, 0, VL_METRIC_SQL2>(p, plan, launch, stream);
     });
     return rc;
 }

@@ -95,13 +95,18 @@ __device__ __forceinline__ float4 vl_load_chunk(const float* __restrict__ row, i
 // registers (largest stride first), levels 4*LPR > h >= 4 are shuffles between lanes, and the
 // last two levels combine the four components of the remaining float4 - the same additions in
 // the same order, so the result is bit-identical.
-template <int LPR, int JP>
+// JU > 0 says only registers j < JU hold data (the rest are zero by construction): adds of
+// a known zero are skipped, which changes nothing (x + 0 == x; the sign of an all-zero sum
+// does not survive vl_finish).
+template <int LPR, int JP, int JU = 0>
 __device__ __forceinline__ float vl_tree_reduce(float4 (&acc)[JP])
 {
+    constexpr int USED = JU > 0 ? JU : JP;
 #pragma unroll
     for (int h = JP / 2; h >= 1; h >>= 1) {
 #pragma unroll
-        for (int j = 0; j < h; ++j) acc[j] = vl_add4(acc[j], acc[j + h]);
+        for (int j = 0; j < h; ++j)
+            if (j + h < USED) acc[j] = vl_add4(acc[j], acc[j + h]);
     }
     float4 a = acc[0];
 #pragma unroll
@@ -112,6 +117,25 @@ __device__ __forceinline__ float vl_tree_reduce(float4 (&acc)[JP])
         a.w = __fadd_rn(a.w, __shfl_down_sync(0xffffffffu, a.w, off, LPR));
     }
     return __fadd_rn(__fadd_rn(a.x, a.z), __fadd_rn(a.y, a.w));
+}
+
+// Exact-fit fast path: the row is exactly LPR*JU 16-byte chunks (dim == 4*LPR*JU <= 1024,
+// aligned), so every lane loads JU chunks with no bounds test; `row` must be a readable row
+// even for a dead candidate (its result is discarded).
+template <int LPR, int JU>
+__device__ __forceinline__ void vl_load_exact(const float* __restrict__ row, int lg, float4 (&xr)[JU])
+{
+    const float4* r4 = reinterpret_cast<const float4*>(row) + lg;
+#pragma unroll
+    for (int j = 0; j < JU; ++j) xr[j] = __ldg(r4 + LPR * j);
+}
+template <int LPR, int JP, int JU, int METRIC>
+__device__ __forceinline__ float vl_exact_distance(const float4 (&xr)[JU], const float4 (&qr)[JU])
+{
+    float4 acc[JP];
+#pragma unroll
+    for (int j = 0; j < JP; ++j) acc[j] = j < JU ? vl_term4<METRIC>(xr[j < JU ? j : 0], qr[j < JU ? j : 0]) : make_float4(0.f, 0.f, 0.f, 0.f);
+    return vl_finish<METRIC>(vl_tree_reduce<LPR, JP, JU>(acc));
 }
 
 // The query-side registers of one lane: chunks lg + LPR*j of the first 1024 elements.
