@@ -144,15 +144,29 @@ typedef struct vl_beam_params {
     int64_t group_rows;        /* rows per batch of the reference's host loop (flags are per batch) */
     uint32_t* changed_flags;   /* [groups, n_checks]: OR of "head changed" at iteration (c+1)*readahead */
     int32_t n_checks;
-    int32_t reserved;
+    int32_t memo_entries;      /* entries of the distance memo per row in flight: a power of two >= 2, or 0 = no memo */
     uint32_t* group_full;      /* [groups]: set when some row of the batch never popped a MAXINT */
     int32_t* status;
+    unsigned long long* memo;  /* [memo_slots, memo_entries] scratch, any contents (see vl_beam_search_plan) */
+    int64_t memo_slots;        /* rows in flight the scratch was sized for: >= blocks * warps_per_block of the plan */
+    unsigned long long* stats; /* optional [16] counters (added to): [1] gathered candidates, [2] search-queue merges,
+                                  [3] visit-queue merges, [6] rows, [7] iterations, [8..13] warp cycles spent in: pop +
+                                  neighbour ids, memo probe, gather, memo update, search-queue merge, visit-queue merge */
+    int32_t flags;             /* bit 0: also accumulate the per-phase cycle counters of `stats` */
+    int32_t reserved;
 } vl_beam_params;
 
 int vl_beam_search(const vl_beam_params* params, void* stream);
 
 /* Bytes of shared memory one warp (= one query row in flight) of vl_beam_search needs for the
- * given shape, and the warps per CTA it will use; for capacity planning and tests. */
+ * given shape, the warps per CTA and the CTAs it will launch.  blocks * warps_per_block is the
+ * number of rows in flight, i.e. the memo_slots a distance memo must provide.
+ *
+ * The memo: during one row's search the same candidate id comes back many times (neighbour
+ * lists of nearby nodes overlap; the reference recomputes its distance every time).  With a
+ * memo the kernel keeps id -> distance of the row's recent candidates in a 2-way table in
+ * global memory (L2-resident) and gathers only the ids it has not met: same bits, a fraction
+ * of the gathers. */
 int vl_beam_search_plan(const vl_beam_params* params, int* smem_per_warp, int* warps_per_block, int* blocks);
 
 #ifdef __cplusplus

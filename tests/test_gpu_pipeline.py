@@ -87,10 +87,12 @@ def test_ann_constructor_is_a_drop_in(c1, built_lib):
     assert (n(clusters.indices[:, 0]) == np.arange(2000)).mean() > 0.99
 
 
-def closest_both(vectors, beams, queries, oq, cfg, exclude=None, metric="cosine", stepwise=False):
+def closest_both(vectors, beams, queries, oq, cfg, exclude=None, metric="cosine", stepwise=False, memo=True):
     from vectorlink_gpu.ann import closest_vectors
     gq = gpu_queue_from(oq)
     config = dict(cfg)
+    if not memo:
+        config["memo"] = False
     if metric != "cosine":
         config["metric"] = metric
     if stepwise:
@@ -140,6 +142,23 @@ def test_fused_closest_vectors_vs_oracle(case, metric, built_lib):
     assert gcount == ocount
     assert np.array_equal(n(gq.indices), oq.indices)
     assert np.array_equal(n(gq.distances), oq.distances)
+
+
+def test_distance_memo_changes_nothing(built_lib):
+    """The fused kernel's id -> distance memo only skips gathers of ids it has already met."""
+    rng = np.random.default_rng(31)
+    vectors = unit(rng, 4000, 64)
+    cfg = oracle.make_config(beam_size=16, visit_queue_factor=2, recall_search_queue_factor=2)
+    kn = oracle.bruteforce_knn(vectors, vectors, 16, exclude_self=True)
+    queries = unit(rng, 50, 64)
+    results = []
+    for memo in (True, False):
+        oq = oracle.initial_search_queue(vectors, queries, cfg)
+        gq, oq, gcount, ocount = closest_both(vectors, kn, queries, oq, cfg, memo=memo)
+        assert gcount == ocount
+        assert np.array_equal(n(gq.indices), oq.indices) and np.array_equal(n(gq.distances), oq.distances)
+        results.append(n(gq.indices))
+    assert np.array_equal(results[0], results[1])
 
 
 @pytest.mark.parametrize("batch", [1, 2, 5])

@@ -35,7 +35,7 @@ constexpr int kBeamWarps = 4;             // most warps (= rows in flight) per C
 constexpr int32_t kHashEmpty = -1;
 
 struct BeamSmem {      // per-warp carve-up, in bytes from the warp's base
-    int cand, sq_a, sq_b, vq_a, vq_b, hash, pop, mpos, total;
+    int cand, sq_a, sq_b, vq_a, vq_b, hash, pop, mpos, todo, total;
     int hash_slots, hash_shift;
 };
 
@@ -55,6 +55,7 @@ __host__ __device__ inline BeamSmem beam_smem_layout(int m, int sq_len, int vq_l
     s.hash = off; off += 4 * slots;
     s.pop = off; off += 4 * 32;
     s.mpos = off; off += 4 * 32;
+    s.todo = off; off += 2 * m;
     s.total = (off + 15) & ~15;
     return s;
 }
@@ -84,6 +85,20 @@ __device__ __forceinline__ bool hash_contains(const int32_t* table, int slots, i
     return false;
 }
 
+// Distance memo: 2-entry buckets of (ordered distance << 32 | id) keys, newest first.
+__device__ __forceinline__ unsigned memo_bucket(uint32_t id, int shift, int buckets)
+{
+    return buckets > 1 ? (id * 2654435761u) >> shift : 0u;
+}
+// A new key goes to way `way` of its bucket (the caller alternates the way between
+// iterations: first-in-first-out over two ways without reading the bucket).  An entry is one
+// aligned 64-bit word, so lanes that collide on a slot can only lose an entry, never pair an
+// id with another id's distance.
+__device__ __forceinline__ void memo_put(vl_key_t* memo, int buckets, int shift, vl_key_t key, int way)
+{
+    memo[2 * (size_t)memo_bucket((uint32_t)key, shift, buckets) + way] = key;
+}
+
 // ascending sort of one 64-bit key per lane across the warp (bitonic network on shuffles)
 __device__ __forceinline__ vl_key_t warp_sort32(vl_key_t k, int lane)
 {
@@ -105,33 +120,56 @@ __device__ __forceinline__ vl_key_t warp_sort32(vl_key_t k, int lane)
 // last), dropping keys already present and repeats; result in `nxt`, cut at len, and the two
 // pointers swapped.  `mpos` is a 32-int scratch of the warp.  Every `want` key is below
 // cur[len-1], so the smallest new distinct key always enters: returns true iff one did.
+// Most offered keys are already in the list (good candidates come back all the time), so the
+// membership test comes first and costs one binary search per offering lane; the common
+// single-survivor case is a plain shift, only several survivors need the warp sort.
 // All 32 lanes call this.
 __device__ __forceinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int len, vl_key_t key, bool want,
                                             int lane, int* mpos)
 {
     const vl_key_t kNone = ~0ull;
-    const unsigned wmask = __ballot_sync(0xffffffffu, want);
-    vl_key_t k;
-    if (__popc(wmask) == 1) {
-        vl_key_t k0 = __shfl_sync(0xffffffffu, key, __ffs(wmask) - 1);
-        k = lane == 0 ? k0 : kNone;
-    } else {
-        k = warp_sort32(want ? key : kNone, lane);
+    int lo = 0;
+    if (want) {   // lo = number of list keys below key
+        int hi = len;
+        while (lo < hi) {
+            int mid = (lo + hi) >> 1;
+            if (cur[mid] < key) lo = mid + 1; else hi = mid;
+        }
+        if (lo < len && cur[lo] == key) want = false;
     }
+    const unsigned wmask = __ballot_sync(0xffffffffu, want);
+    if (!wmask) return false;
+    if (__popc(wmask) == 1) {
+        const int src = __ffs(wmask) - 1;
+        const vl_key_t k0 = __shfl_sync(0xffffffffu, key, src);
+        const int pos = __shfl_sync(0xffffffffu, lo, src);
+        for (int jb = 0; jb < len; jb += 32) {
+            const int j = jb + lane;
+            if (j < len) {
+                const vl_key_t e = cur[j];
+                const int dst = j + (j >= pos);
+                if (dst < len) nxt[dst] = e;
+            }
+        }
+        if (lane == 0) nxt[pos] = k0;
+        __syncwarp();
+        vl_key_t* t = cur; cur = nxt; nxt = t;
+        return true;
+    }
+    // several new keys: order them, drop repeats among them, splice by rank
+    vl_key_t k = warp_sort32(want ? key : kNone, lane);
     bool valid = (k != kNone);
     const vl_key_t prev = __shfl_up_sync(0xffffffffu, k, 1);
     if (lane > 0 && prev == k) valid = false;
-    int lo = 0;
-    if (valid) {   // lo = number of list keys below k
+    lo = 0;
+    if (valid) {
         int hi = len;
         while (lo < hi) {
             int mid = (lo + hi) >> 1;
             if (cur[mid] < k) lo = mid + 1; else hi = mid;
         }
-        if (lo < len && cur[lo] == k) valid = false;
     }
     const unsigned vmask = __ballot_sync(0xffffffffu, valid);
-    if (!vmask) return false;
     const int rank = __popc(vmask & ((1u << lane) - 1u));
     const int nv = __popc(vmask);
     if (valid) mpos[rank] = lo;
@@ -154,7 +192,7 @@ __device__ __forceinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int 
 
 // JU > 0: exact-fit rows (dim == 4*LPR*JU, see vl_load_exact); JU == 0: any dim % 4 == 0.
 template <int LPR, int JP, int JU, int METRIC>
-__global__ void __launch_bounds__(kBeamWarps * 32)
+__global__ void __launch_bounds__(kBeamWarps * 32, 5)
 beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -167,6 +205,13 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
     int32_t* hash = reinterpret_cast<int32_t*>(base + lay.hash);
     int32_t* pop = reinterpret_cast<int32_t*>(base + lay.pop);
     int* mpos = reinterpret_cast<int*>(base + lay.mpos);
+    unsigned short* todo = reinterpret_cast<unsigned short*>(base + lay.todo);
+    // distance memo of this warp's row: memo_entries 64-bit (ordered distance, id) keys as
+    // 2-entry buckets; ~0 = empty.  Only this warp touches its slice.
+    const int memo_buckets = p.memo ? (p.memo_entries >> 1) : 0;
+    int memo_shift = 32;
+    for (int b = memo_buckets; b > 1; b >>= 1) --memo_shift;
+    vl_key_t* memo = p.memo ? p.memo + ((size_t)blockIdx.x * (blockDim.x >> 5) + warp) * (size_t)p.memo_entries : nullptr;
 
     const int wb = p.graph_w, pvc = p.pvc, m_total = p.pvc * p.graph_w;
     const int sq_len = p.sq_len, vq_len = p.vq_len, e_cap = p.seen_cap;
@@ -174,6 +219,9 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
     const int n_run = p.n_iters < k_none ? p.n_iters : k_none;
     const vl_key_t kSent = vl_sentinel_key();
     const uint32_t sent_ord = (uint32_t)(kSent >> 32);
+    const uint32_t kPoppedOrd = 0xffffffffu;                      // above every real ordered distance
+    const vl_key_t kPopped = (vl_key_t)kPoppedOrd << 32;
+    const float inv_wb = 1.0f / (float)p.graph_w;
 
     const int wpb = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * wpb + warp;
@@ -192,12 +240,17 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         // ---- prologue: Queue.insert of the seeds into an empty queue (queue.py:37-61) ----
         for (int i = lane; i < sq_len; i += 32) sq[i] = kSent;
         for (int i = lane; i < lay.hash_slots; i += 32) hash[i] = kHashEmpty;
+        if (memo) {
+            ulonglong2* m2 = reinterpret_cast<ulonglong2*>(memo);
+            for (int i = lane; i < memo_buckets; i += 32) m2[i] = make_ulonglong2(~0ull, ~0ull);
+        }
         __syncwarp();
         for (int c0 = 0; c0 < p.seed_cols; c0 += 32) {
             int c = c0 + lane;
             vl_key_t key = kSent;
             if (c < p.seed_cols)
                 key = vl_entry_key(__ldg(p.seed_dist + row * p.seed_ld + c), __ldg(p.seed_ids + row * p.seed_ld + c));
+            if (memo && key != kSent) memo_put(memo, memo_buckets, memo_shift, key, 0);   // a seed's distance is known
             bool want = key < sq[sq_len - 1];
             if (__any_sync(0xffffffffu, want)) merge_chunk(sq, sq_n, sq_len, key, want, lane, mpos);
         }
@@ -209,6 +262,11 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         __syncwarp();
 
         bool always_full = true;
+        unsigned long long st_todo = 0, st_sm = 0, st_vm = 0, st_iter = 0;
+        long long tk[6] = {0, 0, 0, 0, 0, 0};     // cycles per phase when p.stats is given
+        const bool timing = p.stats != nullptr && (p.flags & 1);
+        long long t_prev = timing ? clock64() : 0;
+#define VL_PHASE(i) do { if (timing) { long long t_now = clock64(); tk[i] += t_now - t_prev; t_prev = t_now; } } while (0)
         const int32_t self_id = p.self_base >= 0 ? (int32_t)(p.self_base + row) : VL_MAXINT;
         const int32_t* excl = p.exclude_w > 0 ? p.exclude + row * (int64_t)p.exclude_w : nullptr;
         const int64_t group = p.group_rows > 0 ? row / p.group_rows : 0;
@@ -217,60 +275,121 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         for (int k = 1; k <= n_run; ++k) {
             const int first = (k - 1) * pvc;
             const bool seen_live = first < e_cap;    // utils.py:62-69
+            const int ncopy = seen_live ? ((e_cap - first) < pvc ? (e_cap - first) : pvc) : 0;
             // ---- pop_n_ids (queue.py:87-95) ----
             {
                 vl_key_t head = lane < pvc ? vq[lane] : kSent;
-                if (lane < pvc) pop[lane] = vl_key_id(head);
+                int32_t node = vl_key_id(head);
+                if (lane < pvc) {
+                    if (node != VL_MAXINT && (node < 0 || (int64_t)node >= p.n)) {
+                        atomicOr(p.status, VL_STATUS_BAD_ID);
+                        node = VL_MAXINT;
+                    }
+                    pop[lane] = node;
+                    // An id that enters `seen` now can never enter the visit queue again, and the
+                    // search queue only looks at newly gathered ids: from here on its memo entry
+                    // only has to say "popped" (an ordered distance above every real one).
+                    if (memo && lane < ncopy && node != VL_MAXINT) {
+                        vl_key_t* bk = memo + 2 * (size_t)memo_bucket((uint32_t)node, memo_shift, memo_buckets);
+                        const vl_key_t e0 = bk[0], e1 = bk[1];
+                        if ((uint32_t)e0 == (uint32_t)node) bk[0] = kPopped | (uint32_t)node;
+                        else if ((uint32_t)e1 == (uint32_t)node) bk[1] = kPopped | (uint32_t)node;
+                    }
+                }
                 for (int i = lane; i < vq_len; i += 32) vq_n[i] = (i + pvc < vq_len) ? vq[i + pvc] : kSent;
                 __syncwarp();
                 vl_key_t* t = vq; vq = vq_n; vq_n = t;
             }
-            // ---- neighbour ids of the popped nodes (kernels.py:244) ----
-            for (int v = 0; v < pvc; ++v) {
-                int32_t node = pop[v];
-                if (node != VL_MAXINT && (node < 0 || (int64_t)node >= p.n)) {
-                    if (lane == 0) atomicOr(p.status, VL_STATUS_BAD_ID);
-                    node = VL_MAXINT;
-                }
-                const int32_t* grow = p.graph + (int64_t)(node == VL_MAXINT ? 0 : node) * wb;
-                for (int j = lane; j < wb; j += 32) {
-                    int32_t id = VL_MAXINT;
-                    if (node != VL_MAXINT) {
-                        id = __ldg(grow + j);
-                        if (id != VL_MAXINT && (id < 0 || (int64_t)id >= p.n)) { atomicOr(p.status, VL_STATUS_BAD_ID); id = VL_MAXINT; }
+            VL_PHASE(0);   // pop
+            // ---- neighbour ids of the popped nodes (kernels.py:244), then which of them need a
+            // gather: live ids the memo does not know.  Four chunks of 32 candidates per round so
+            // that the graph-row loads, and then the memo loads, of a round are in flight together.
+            int n_todo = 0;
+            const bool raw_iteration = p.dump_last && k == p.n_iters;   // needs every real distance
+            for (int cb = 0; cb < m_total; cb += 128) {
+                int32_t idr[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = cb + 32 * u + lane;
+                    idr[u] = VL_MAXINT;
+                    if (c < m_total) {
+                        const int v = __float2int_rz(((float)c + 0.5f) * inv_wb);
+                        const int32_t node = pop[v];
+                        if (node != VL_MAXINT) idr[u] = __ldg(p.graph + (int64_t)node * wb + (c - v * wb));
                     }
-                    cand[v * wb + j] = make_uint2((uint32_t)id, sent_ord);
+                }
+                ulonglong2 bk[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (idr[u] != VL_MAXINT && (idr[u] < 0 || (int64_t)idr[u] >= p.n)) {
+                        atomicOr(p.status, VL_STATUS_BAD_ID);
+                        idr[u] = VL_MAXINT;
+                    }
+                    bk[u] = make_ulonglong2(~0ull, ~0ull);
+                    if (memo && idr[u] != VL_MAXINT)
+                        bk[u] = *reinterpret_cast<const ulonglong2*>(memo + 2 * (size_t)memo_bucket((uint32_t)idr[u], memo_shift, memo_buckets));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = cb + 32 * u + lane;
+                    const uint32_t id = (uint32_t)idr[u];
+                    bool need = (idr[u] != VL_MAXINT);
+                    uint32_t ord = sent_ord;
+                    if (need) {
+                        if ((uint32_t)bk[u].x == id) { ord = (uint32_t)(bk[u].x >> 32); need = false; }
+                        else if ((uint32_t)bk[u].y == id) { ord = (uint32_t)(bk[u].y >> 32); need = false; }
+                        if (!need && raw_iteration && ord == kPoppedOrd) need = true;
+                    }
+                    if (c < m_total) cand[c] = make_uint2(id, ord);
+                    const unsigned mask = __ballot_sync(0xffffffffu, need);
+                    if (need) todo[n_todo + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)c;
+                    n_todo += __popc(mask);
                 }
             }
             __syncwarp();
-            // ---- gathered distances (kernels.py:248-257), two steps in flight ----
-            for (int m0 = 0; m0 < m_total; m0 += 2 * G) {
-                const int ma = m0 + g, mb = m0 + G + g;
-                int32_t ida = ma < m_total ? (int32_t)cand[ma].x : VL_MAXINT;
-                int32_t idb = mb < m_total ? (int32_t)cand[mb].x : VL_MAXINT;
-                const bool la = ida != VL_MAXINT, lb = idb != VL_MAXINT;
-                const float* ra = p.vectors + (int64_t)(la ? ida : 0) * p.dim;
-                const float* rb = p.vectors + (int64_t)(lb ? idb : 0) * p.dim;
-                float da, db;
+            st_todo += n_todo;
+            st_iter += 1;
+            VL_PHASE(1);   // neighbour ids + memo probe
+            // ---- gathered distances (kernels.py:248-257): G rows per step, U steps in flight ----
+            constexpr int U = (JQ <= 4) ? 2 : 1;
+            for (int t0 = 0; t0 < n_todo; t0 += U * G) {
+                bool live[U];
+                int mi[U];
+                const float* rp[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int t = t0 + u * G + g;
+                    live[u] = t < n_todo;
+                    mi[u] = live[u] ? todo[t] : 0;
+                    const int32_t id = live[u] ? (int32_t)cand[mi[u]].x : 0;
+                    rp[u] = p.vectors + (int64_t)id * p.dim;
+                }
+                float dd[U];
                 if constexpr (JU > 0) {
-                    float4 xa[JU], xb[JU];
-                    vl_load_exact<LPR, JU>(ra, lg, xa);
-                    vl_load_exact<LPR, JU>(rb, lg, xb);
-                    da = vl_exact_distance<LPR, JP, JU, METRIC>(xa, qr);
-                    db = vl_exact_distance<LPR, JP, JU, METRIC>(xb, qr);
+                    float4 x[U][JU];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) vl_load_exact<LPR, JU>(rp[u], lg, x[u]);
+#pragma unroll
+                    for (int u = 0; u < U; ++u) dd[u] = vl_exact_distance<LPR, JP, JU, METRIC>(x[u], qr);
                 } else {
-                    float4 xa[JP], xb[JP];
-                    vl_load_row<LPR, JP, true>(ra, p.dim, lg, la, xa);
-                    vl_load_row<LPR, JP, true>(rb, p.dim, lg, lb, xb);
-                    da = vl_row_distance<LPR, JP, METRIC, true>(xa, qr, ra, q, p.dim, lg, la);
-                    db = vl_row_distance<LPR, JP, METRIC, true>(xb, qr, rb, q, p.dim, lg, lb);
+                    float4 x[U][JP];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) vl_load_row<LPR, JP, true>(rp[u], p.dim, lg, live[u], x[u]);
+#pragma unroll
+                    for (int u = 0; u < U; ++u) dd[u] = vl_row_distance<LPR, JP, METRIC, true>(x[u], qr, rp[u], q, p.dim, lg, live[u]);
                 }
                 if (lg == 0) {
-                    if (la) cand[ma].y = vl_ord(da);
-                    if (lb) cand[mb].y = vl_ord(db);
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+                        if (live[u]) cand[mi[u]].y = vl_ord(dd[u]);
                 }
             }
             __syncwarp();
+            VL_PHASE(2);   // gather
+            if (memo) {   // remember what was just computed
+                for (int t = lane; t < n_todo; t += 32) memo_put(memo, memo_buckets, memo_shift, candk[todo[t]], k & 1);
+                __syncwarp();
+            }
             // ---- search_queue.insert(..., exclude) (ann.py:75-80) ----
             if (p.dump_last && k == p.n_iters) {
                 // leave this insert to the caller's full-row sort: head, then the raw candidates
@@ -299,52 +418,120 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 dumped = true;
                 break;
             }
+            VL_PHASE(3);   // memo put
+            // Only candidates gathered in this iteration are offered: an id the memo already knew
+            // was offered when it was first gathered, and the search queue's cut-off only falls, so
+            // offering it again can neither add nor move anything.
             bool changed = false;
             vl_key_t cut = sq[sq_len - 1];
-            for (int c0 = 0; c0 < m_total; c0 += 32) {
-                const int c = c0 + lane;
-                vl_key_t key = c < m_total ? candk[c] : kSent;
+            for (int t0 = 0; t0 < n_todo; t0 += 32) {
+                const int t = t0 + lane;
+                vl_key_t key = t < n_todo ? candk[todo[t]] : kSent;
                 bool want = key < cut;
                 if (!__any_sync(0xffffffffu, want)) continue;
                 if (want) {
                     int32_t id = vl_key_id(key);
                     if (id == self_id) want = false;
                     else if (excl)
-                        for (int t = 0; t < p.exclude_w; ++t) {   // kernels.py:478-488
-                            int32_t x = excl[t];
-                            if (x == VL_MAXINT) break;
-                            if (x == id) { want = false; break; }
+                        for (int x = 0; x < p.exclude_w; ++x) {   // kernels.py:478-488
+                            int32_t ex = excl[x];
+                            if (ex == VL_MAXINT) break;
+                            if (ex == id) { want = false; break; }
                         }
                 }
                 if (!__any_sync(0xffffffffu, want)) continue;
                 changed |= merge_chunk(sq, sq_n, sq_len, key, want, lane, mpos);
+                st_sm += 1;
                 cut = sq[sq_len - 1];
             }
+            VL_PHASE(4);   // search-queue merge
             if (changed && (k % p.readahead) == 0 && lane == 0) {
                 int chk = k / p.readahead - 1;
                 if (chk < p.n_checks) atomicOr(p.changed_flags + group * p.n_checks + chk, 1u);
             }
             // ---- add_new_to_seen_ (utils.py:61-82) + visit_queue.insert(..., exclude=seen) ----
             if (seen_live) {
-                const int ncopy = (e_cap - first) < pvc ? (e_cap - first) : pvc;
                 int32_t mine = lane < ncopy ? pop[lane] : 0;
                 if (lane < ncopy && mine != VL_MAXINT) hash_insert(hash, lay.hash_slots, lay.hash_shift, mine, p.status);
                 if (__any_sync(0xffffffffu, lane < ncopy && mine == VL_MAXINT)) always_full = false;
                 __syncwarp();
-                vl_key_t vcut = vq[vq_len - 1];
-                for (int c0 = 0; c0 < m_total; c0 += 32) {
-                    const int c = c0 + lane;
-                    vl_key_t key = c < m_total ? candk[c] : kSent;
-                    bool want = key < vcut;
-                    if (!__any_sync(0xffffffffu, want)) continue;
-                    if (want && hash_contains(hash, lay.hash_slots, lay.hash_shift, vl_key_id(key))) want = false;
-                    if (!__any_sync(0xffffffffu, want)) continue;
-                    merge_chunk(vq, vq_n, vq_len, key, want, lane, mpos);
-                    vcut = vq[vq_len - 1];
+                // The popped entries left `free` slots, so the new queue is: every candidate
+                // below the largest kept key T0 that is neither visited nor already queued (class A,
+                // merged by rank), then - only if slots remain - the smallest unvisited candidates
+                // above T0 (class B, appended one by one in rising order).  Same queue as offering
+                // every candidate, without sorting the many that are already in it.
+                int n_old = 0;
+                for (int i0 = 0; i0 < vq_len; i0 += 32)
+                    n_old += __popc(__ballot_sync(0xffffffffu, i0 + lane < vq_len && vq[i0 + lane] != kSent));
+#ifdef VL_OLD_VISIT
+                if (false) {
+#else
+                if (n_old > 0 && vq_len - n_old <= 8) {
+#endif
+                    const vl_key_t t0key = vq[n_old - 1];
+                    int n_a = 0;
+                    for (int c0 = 0; c0 < m_total; c0 += 32) {
+                        const int c = c0 + lane;
+                        const bool in_a = c < m_total && candk[c] < t0key;
+                        const unsigned mask = __ballot_sync(0xffffffffu, in_a);
+                        if (in_a) todo[n_a + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)c;
+                        n_a += __popc(mask);
+                    }
+                    __syncwarp();
+                    vl_key_t vcut = vq[vq_len - 1];
+                    for (int t0 = 0; t0 < n_a; t0 += 32) {
+                        const int t = t0 + lane;
+                        vl_key_t key = t < n_a ? candk[todo[t]] : kSent;
+                        bool want = key < vcut;
+                        if (want && hash_contains(hash, lay.hash_slots, lay.hash_shift, vl_key_id(key))) want = false;
+                        if (!__any_sync(0xffffffffu, want)) continue;
+                        merge_chunk(vq, vq_n, vq_len, key, want, lane, mpos);
+                        st_vm += 1;
+                        vcut = vq[vq_len - 1];
+                    }
+                    int n_real = 0;
+                    for (int i0 = 0; i0 < vq_len; i0 += 32)
+                        n_real += __popc(__ballot_sync(0xffffffffu, i0 + lane < vq_len && vq[i0 + lane] != kSent));
+                    vl_key_t last = t0key;
+                    while (n_real < vq_len) {
+                        vl_key_t best = ~0ull;
+                        for (int c = lane; c < m_total; c += 32) {
+                            const vl_key_t kk = candk[c];
+                            if (kk > last && kk < kSent && kk < best) best = kk;
+                        }
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) {
+                            const vl_key_t o = __shfl_xor_sync(0xffffffffu, best, off);
+                            best = o < best ? o : best;
+                        }
+                        if (best == ~0ull) break;
+                        last = best;
+                        if (hash_contains(hash, lay.hash_slots, lay.hash_shift, vl_key_id(best))) continue;
+                        if (lane == 0) vq[n_real] = best;
+                        ++n_real;
+                        st_vm += 1;
+                    }
+                    __syncwarp();
+                } else {
+                    // an (almost) empty queue: offer every candidate, 32 at a time
+                    vl_key_t vcut = vq[vq_len - 1];
+                    for (int c0 = 0; c0 < m_total; c0 += 32) {
+                        const int c = c0 + lane;
+                        vl_key_t key = c < m_total ? candk[c] : kSent;
+                        bool want = key < vcut;
+                        if (!__any_sync(0xffffffffu, want)) continue;
+                        if (want && hash_contains(hash, lay.hash_slots, lay.hash_shift, vl_key_id(key))) want = false;
+                        if (!__any_sync(0xffffffffu, want)) continue;
+                        merge_chunk(vq, vq_n, vq_len, key, want, lane, mpos);
+                        st_vm += 1;
+                        vcut = vq[vq_len - 1];
+                    }
                 }
             }
+            VL_PHASE(5);   // seen update + visit-queue merge
         }
 
+        VL_PHASE(5);       // visit-queue merge of the last iteration + epilogue
         if (!dumped) {
             for (int i = lane; i < p.out_cols; i += 32) {
                 vl_key_t key = i < sq_len ? sq[i] : kSent;
@@ -353,6 +540,15 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             }
         }
         if (always_full && lane == 0) atomicOr(p.group_full + group, 1u);
+        if (p.stats && lane == 0) {
+            atomicAdd(p.stats + 1, st_todo);
+            atomicAdd(p.stats + 2, st_sm);
+            atomicAdd(p.stats + 3, st_vm);
+            atomicAdd(p.stats + 6, 1ull);
+            atomicAdd(p.stats + 7, st_iter);
+            if (timing)
+                for (int i = 0; i < 6; ++i) atomicAdd(p.stats + 8 + i, (unsigned long long)tk[i]);
+        }
         __syncwarp();
     }
 }
@@ -382,6 +578,9 @@ int plan_and_launch(const vl_beam_params& p, BeamPlan& plan, bool launch, cudaSt
     int64_t want = (p.rows + plan.warps - 1) / plan.warps;
     int64_t resident = (int64_t)sms * per_sm;   // one resident wave; rows beyond it are strided
     plan.blocks = (int)(want < resident ? want : resident);
+    if (launch && p.memo)
+        VL_CHECK_ARG(p.memo_slots >= (int64_t)plan.blocks * plan.warps, "vl_beam_search: memo has %lld slots, the launch keeps %lld rows in flight",
+                     (long long)p.memo_slots, (long long)plan.blocks * plan.warps);
     if (launch && plan.blocks > 0) {
         kernel<<<plan.blocks, plan.warps * 32, plan.smem, stream>>>(p, plan.lay);
         VL_CHECK_LAUNCH("beam_search_kernel");
@@ -409,6 +608,9 @@ int beam_dispatch(const vl_beam_params* pp, BeamPlan& plan, bool launch, cudaStr
     VL_CHECK_ARG(!p.dump_last || p.n_iters <= (p.seen_cap + p.pvc - 1) / p.pvc + 1, "vl_beam_search: dump_last past the last productive iteration");
     VL_CHECK_ARG(p.exclude_w == 0 || p.exclude, "vl_beam_search: exclusion width without a list");
     VL_CHECK_ARG(p.n_checks >= 0 && p.group_rows >= 0, "vl_beam_search: bad flag shape");
+    VL_CHECK_ARG(p.pvc * (int64_t)p.graph_w <= 65535, "vl_beam_search: %d candidates per iteration exceed 65535", p.pvc * p.graph_w);
+    VL_CHECK_ARG(!p.memo || (p.memo_entries >= 2 && (p.memo_entries & (p.memo_entries - 1)) == 0 && (uintptr_t)p.memo % 16 == 0),
+                 "vl_beam_search: memo_entries must be a power of two >= 2 and the memo 16-byte aligned");
     if (p.rows == 0) { plan.blocks = 0; plan.warps = kBeamWarps; plan.lay = beam_smem_layout(p.pvc * p.graph_w, p.sq_len, p.vq_len, p.seen_cap); return 0; }
     VlShape shape = vl_pick_shape(p.dim);
     int rc = 0;
@@ -419,12 +621,12 @@ int beam_dispatch(const vl_beam_params* pp, BeamPlan& plan, bool launch, cudaStr
         if (p.metric == VL_METRIC_COSINE) return plan_and_launch<L, J, U, VL_METRIC_COSINE>(p, plan, launch, stream); \
         return plan_and_launch<L, J, U, VL_METRIC_SQL2>(p, plan, launch, stream);                      \
     }
-    VL_EXACT(8, 2, 2)     // dim 64
-    VL_EXACT(8, 4, 3)     // dim 96
-    VL_EXACT(8, 4, 4)     // dim 128
-    VL_EXACT(16, 4, 4)    // dim 256
-    VL_EXACT(32, 4, 3)    // dim 384
-    VL_EXACT(32, 4, 4)    // dim 512
+    VL_EXACT(4, 4, 4)     // dim 64
+    VL_EXACT(4, 8, 6)     // dim 96
+    VL_EXACT(4, 8, 8)     // dim 128
+    VL_EXACT(8, 8, 8)     // dim 256
+    VL_EXACT(16, 8, 6)    // dim 384
+    VL_EXACT(16, 8, 8)    // dim 512
     VL_EXACT(32, 8, 6)    // dim 768
     VL_EXACT(32, 8, 8)    // dim 1024
 #undef VL_EXACT

@@ -90,8 +90,8 @@ __device__ __forceinline__ float4 vl_load_chunk(const float* __restrict__ row, i
 
 // The reference's sum (kernels.py:38-72 + 27-35) is a halving tree over a 1024-slot buffer:
 // slot t += slot t+h for h = 512 ... 1, after slots 1024k+t were folded onto t in rising k.
-// A row is spread over LPR lanes as 16-byte chunks, lane l holding chunks l + LPR*j, j < JP
-// (LPR*JP*4 >= min(dim,1024)).  Then tree levels h >= 4*LPR are adds between a lane's own
+// A row is spread over LPR lanes (4, 8, 16 or 32) as 16-byte chunks, lane l holding chunks
+// l + LPR*j, j < JP (LPR*JP*4 >= min(dim,1024)).  Then tree levels h >= 4*LPR are adds between a lane's own
 // registers (largest stride first), levels 4*LPR > h >= 4 are shuffles between lanes, and the
 // last two levels combine the four components of the remaining float4 - the same additions in
 // the same order, so the result is bit-identical.
@@ -129,13 +129,79 @@ __device__ __forceinline__ void vl_load_exact(const float* __restrict__ row, int
 #pragma unroll
     for (int j = 0; j < JU; ++j) xr[j] = __ldg(r4 + LPR * j);
 }
+// Packed fp32x2 arithmetic of sm_100 (add/sub/mul.rn.f32x2): two IEEE round-to-nearest
+// operations per instruction, the same bits as the scalar intrinsics, half the issue slots.
+typedef unsigned long long vl_f2;
+__device__ __forceinline__ vl_f2 vl_f2_pack(float lo, float hi)
+{
+    vl_f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void vl_f2_unpack(vl_f2 v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ vl_f2 vl_f2_add(vl_f2 a, vl_f2 b)
+{
+    vl_f2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ vl_f2 vl_f2_sub(vl_f2 a, vl_f2 b)
+{
+    vl_f2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// Products stay scalar: ptxas 12.9 contracts a packed multiply with the packed add that
+// consumes it into one packed FMA (one rounding instead of two) even when both carry .rn,
+// which would break bit parity; a scalar FMUL feeding a packed add is left alone.
+template <int METRIC>
+__device__ __forceinline__ vl_f2 vl_f2_term(float ax, float ay, float bx, float by)
+{
+    if (METRIC == VL_METRIC_COSINE) return vl_f2_pack(__fmul_rn(ax, bx), __fmul_rn(ay, by));
+    float dx, dy;
+    vl_f2_unpack(vl_f2_sub(vl_f2_pack(ax, ay), vl_f2_pack(bx, by)), dx, dy);
+    return vl_f2_pack(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+}
+
+// Exact-fit distance on packed pairs: (x,y) and (z,w) of every chunk travel as fp32x2 through
+// the differences, the register fold and the lane shuffles; the order of additions is that of
+// vl_tree_reduce.
 template <int LPR, int JP, int JU, int METRIC>
 __device__ __forceinline__ float vl_exact_distance(const float4 (&xr)[JU], const float4 (&qr)[JU])
 {
+#ifdef VL_NO_F2
     float4 acc[JP];
 #pragma unroll
     for (int j = 0; j < JP; ++j) acc[j] = j < JU ? vl_term4<METRIC>(xr[j < JU ? j : 0], qr[j < JU ? j : 0]) : make_float4(0.f, 0.f, 0.f, 0.f);
     return vl_finish<METRIC>(vl_tree_reduce<LPR, JP, JU>(acc));
+#endif
+    vl_f2 axy[JU], azw[JU];
+#pragma unroll
+    for (int j = 0; j < JU; ++j) {
+        axy[j] = vl_f2_term<METRIC>(xr[j].x, xr[j].y, qr[j].x, qr[j].y);
+        azw[j] = vl_f2_term<METRIC>(xr[j].z, xr[j].w, qr[j].z, qr[j].w);
+    }
+#pragma unroll
+    for (int h = JP / 2; h >= 1; h >>= 1) {
+#pragma unroll
+        for (int j = 0; j < h; ++j)
+            if (j + h < JU) {
+                axy[j] = vl_f2_add(axy[j], axy[j + h]);
+                azw[j] = vl_f2_add(azw[j], azw[j + h]);
+            }
+    }
+    vl_f2 xy = axy[0], zw = azw[0];
+#pragma unroll
+    for (int off = LPR / 2; off >= 1; off >>= 1) {
+        xy = vl_f2_add(xy, __shfl_down_sync(0xffffffffu, xy, off, LPR));
+        zw = vl_f2_add(zw, __shfl_down_sync(0xffffffffu, zw, off, LPR));
+    }
+    float lo, hi;
+    vl_f2_unpack(vl_f2_add(xy, zw), lo, hi);       // (x+z, y+w)
+    return vl_finish<METRIC>(__fadd_rn(lo, hi));
 }
 
 // The query-side registers of one lane: chunks lg + LPR*j of the first 1024 elements.
@@ -199,21 +265,23 @@ static inline VlShape vl_pick_shape(int dim)
 {
     int chunks = (dim + 3) / 4;
     if (chunks > 256) chunks = 256;
-    if (chunks <= 8) return {8, 1};
-    if (chunks <= 16) return {8, 2};
-    if (chunks <= 32) return {8, 4};
-    if (chunks <= 64) return {16, 4};
-    if (chunks <= 128) return {32, 4};
+    if (chunks <= 4) return {4, 1};
+    if (chunks <= 8) return {4, 2};
+    if (chunks <= 16) return {4, 4};
+    if (chunks <= 32) return {4, 8};
+    if (chunks <= 64) return {8, 8};
+    if (chunks <= 128) return {16, 8};
     return {32, 8};
 }
 
 #define VL_DISPATCH_SHAPE(shape, ...)                                                   \
     do {                                                                                \
-        if ((shape).lpr == 8 && (shape).jp == 1) { constexpr int LPR = 8, JP = 1; __VA_ARGS__ }        \
-        else if ((shape).lpr == 8 && (shape).jp == 2) { constexpr int LPR = 8, JP = 2; __VA_ARGS__ }   \
-        else if ((shape).lpr == 8 && (shape).jp == 4) { constexpr int LPR = 8, JP = 4; __VA_ARGS__ }   \
-        else if ((shape).lpr == 16 && (shape).jp == 4) { constexpr int LPR = 16, JP = 4; __VA_ARGS__ } \
-        else if ((shape).lpr == 32 && (shape).jp == 4) { constexpr int LPR = 32, JP = 4; __VA_ARGS__ } \
+        if ((shape).lpr == 4 && (shape).jp == 1) { constexpr int LPR = 4, JP = 1; __VA_ARGS__ }        \
+        else if ((shape).lpr == 4 && (shape).jp == 2) { constexpr int LPR = 4, JP = 2; __VA_ARGS__ }   \
+        else if ((shape).lpr == 4 && (shape).jp == 4) { constexpr int LPR = 4, JP = 4; __VA_ARGS__ }   \
+        else if ((shape).lpr == 4 && (shape).jp == 8) { constexpr int LPR = 4, JP = 8; __VA_ARGS__ }   \
+        else if ((shape).lpr == 8 && (shape).jp == 8) { constexpr int LPR = 8, JP = 8; __VA_ARGS__ }   \
+        else if ((shape).lpr == 16 && (shape).jp == 8) { constexpr int LPR = 16, JP = 8; __VA_ARGS__ } \
         else { constexpr int LPR = 32, JP = 8; __VA_ARGS__ }                            \
     } while (0)
 

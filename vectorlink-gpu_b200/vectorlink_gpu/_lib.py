@@ -39,8 +39,10 @@ class BeamParams(ctypes.Structure):
         ("out_cols", ctypes.c_int32), ("n_iters", ctypes.c_int32), ("readahead", ctypes.c_int32),
         ("dump_last", ctypes.c_int32), ("exclude_w", ctypes.c_int32),
         ("exclude", ctypes.c_void_p), ("self_base", ctypes.c_int64), ("group_rows", ctypes.c_int64),
-        ("changed_flags", ctypes.c_void_p), ("n_checks", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("changed_flags", ctypes.c_void_p), ("n_checks", ctypes.c_int32), ("memo_entries", ctypes.c_int32),
         ("group_full", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("memo", ctypes.c_void_p), ("memo_slots", ctypes.c_int64), ("stats", ctypes.c_void_p),
+        ("flags", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 

@@ -29,6 +29,10 @@ FUSED_MAX_SMEM_PER_ROW = 200 * 1024
 # When set to a list, every fused-kernel launch appends its CUDA events (recorded on the
 # launching stream) and its count of distance evaluations: the benchmark's roofline figures.
 PROFILE = None
+# When set to an int64 CUDA tensor of 16 zeros, the fused kernel adds its work counters and
+# per-phase warp cycles to it (layout: `stats` in include/vlgpu.h).
+STATS = None
+STATS_TIMERS = False
 
 
 def _metric_of(config: Dict):
@@ -99,6 +103,24 @@ def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len
     p.n_checks = flags.size(1)
     p.group_full = full.data_ptr()
     p.status = _lib.status_word(vectors.device).data_ptr()
+    p.memo = 0
+    p.memo_entries = 0
+    p.memo_slots = 0
+    p.stats = STATS.data_ptr() if STATS is not None else 0
+    p.flags = 1 if (STATS is not None and STATS_TIMERS) else 0
+    if config.get("memo", True):
+        # id -> distance memo of each row in flight (scratch; the kernel clears a row's slice)
+        smem, warps, blocks = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+        check(lib().vl_beam_search_plan(ctypes.byref(p), ctypes.byref(smem), ctypes.byref(warps), ctypes.byref(blocks)),
+              "vl_beam_search_plan")
+        entries = 1024
+        while entries < 12 * p.seen_cap and entries < 16384:
+            entries *= 2
+        slots = max(1, warps.value * blocks.value)
+        memo = _memo_buffer(vectors.device, slots * entries)
+        p.memo = memo.data_ptr()
+        p.memo_entries = entries
+        p.memo_slots = slots
     if PROFILE is not None:
         start = torch.cuda.Event(enable_timing=True)
         end = torch.cuda.Event(enable_timing=True)
@@ -109,6 +131,19 @@ def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len
         k_none = (p.seen_cap + pvc - 1) // pvc + 1
         PROFILE.append({"start": start, "end": end, "rows": int(p.rows), "graph_w": int(p.graph_w),
                         "iterations": int(min(n_iters, k_none)), "evals": int(p.rows) * min(n_iters, k_none) * pvc * int(p.graph_w)})
+
+
+_memo_cache = {}
+
+
+def _memo_buffer(device, words: int) -> Tensor:
+    """A reusable int64 scratch tensor of at least `words` entries on `device`."""
+    key = _lib._device_key(device)
+    buf = _memo_cache.get(key)
+    if buf is None or buf.numel() < words:
+        buf = torch.empty(words, dtype=torch.int64, device=key)
+        _memo_cache[key] = buf
+    return buf
 
 
 def _natural_end(flag_row: List[int], config: Dict) -> int:
