@@ -200,7 +200,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="c2")
-    ap.add_argument("--n", type=int, default=0, help="override the vector count (per GPU)")
+    ap.add_argument("--vectors", dest="n", type=int, default=0, help="override the vector count (per GPU)")
     ap.add_argument("--sample", type=int, default=0, help="vectors in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--loops", type=int, default=0, help="override optimization_loops")
@@ -234,21 +234,37 @@ def main():
     kw = ann_kwargs(w)
     if args.loops:
         kw["optimization_loops"] = args.loops
-    # weak scaling: every rank owns its own shard of w["n"] vectors (different seed per rank);
-    # shards are independent in the build, so there is no data-path collective in a step
-    vectors, queries = make_data(w, w["n"], dev, seed=rank)
-    n, dim = vectors.shape
+    # weak scaling: the job is world x w["n"] vectors; rank r starts with rows [r*n, (r+1)*n) in its
+    # HBM.  A step all-gathers the shards and runs the build with every round's rows split across
+    # the ranks (ShardedANN mode "rows": the graph a single GPU would build over the whole set).
+    n = w["n"]
+    if world > 1:
+        full, queries = make_data(w, n * world, dev, seed=0)
+        vectors = full[rank * n:(rank + 1) * n].clone()
+        del full
+        torch.cuda.empty_cache()
+    else:
+        vectors, queries = make_data(w, n, dev, seed=0)
+    dim = vectors.size(1)
     host_vectors = torch.empty((n, dim), dtype=torch.float32, pin_memory=True)
     host_vectors.copy_(vectors)
     host_beams = torch.empty((n, kw["beam_size"]), dtype=torch.int32, pin_memory=True)
     host_dist = torch.empty((n, kw["beam_size"]), dtype=torch.float32, pin_memory=True)
 
+    if world > 1:
+        from vectorlink_gpu.sharded import ShardedANN
+
+    def build(v):
+        if world > 1:
+            return ShardedANN(v, group=dist.group.WORLD, mode="rows", **kw)
+        return ANN(vectors=v, **kw)
+
     def step_device():
-        return ANN(vectors=vectors, **kw)
+        return build(vectors)
 
     def step_e2e():
         v = host_vectors.to(dev, non_blocking=True)
-        a = ANN(vectors=v, **kw)
+        a = build(v)
         host_beams.copy_(a.beams, non_blocking=True)
         host_dist.copy_(a.distances, non_blocking=True)
         torch.cuda.synchronize(dev)
@@ -282,7 +298,7 @@ def main():
     # the dominant kernel: the fused beam search over all rows (one launch per build round)
     k_ms = [p["start"].elapsed_time(p["end"]) for p in profile]
     k_evals = [p["evals"] for p in profile]
-    big = [i for i, p in enumerate(profile) if p["rows"] == n]
+    big = [i for i, p in enumerate(profile) if p["rows"] >= min(n, 10_000)]
     bytes_per_eval = 4 * dim + 12
     if big:
         ach = sum(k_evals[i] for i in big) * bytes_per_eval / (sum(k_ms[i] for i in big) * 1e-3) / 1e9
@@ -303,15 +319,20 @@ def main():
     barrier()
     e2e_ms = e0.elapsed_time(e1) if not args.quick else float("nan")
 
-    # search over the built graph
-    sq = ann.search(queries)
+    # search over the built graph (data-parallel over the ranks when there are several)
+    def do_search():
+        if world > 1:
+            return ann.search(queries)[0]
+        return ann.search(queries).indices
+
+    found = do_search()
     barrier()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = max(3, args.steps)
     vl_ann.PROFILE = []
     s0.record()
     for _ in range(reps):
-        sq = ann.search(queries)
+        found = do_search()
     s1.record()
     barrier()
     sprof = vl_ann.PROFILE
@@ -321,11 +342,12 @@ def main():
     s_evals = sum(p["evals"] for p in sprof) / reps
     recall = graph_recall = None
     if not args.quick:
-        truth = brute_force_topk(vectors, queries, 10, w["metric"])
-        recall = recall_at_k(sq.indices, truth, 10)
-        gsample = min(n, 10_000)
-        gtruth = brute_force_topk(vectors, vectors[:gsample], 11, w["metric"])[:, 1:]
-        graph_recall = recall_at_k(ann.beams[:gsample], gtruth, 10)
+        index = ann.index if world > 1 else ann
+        truth = brute_force_topk(index.vectors, queries, 10, w["metric"])
+        recall = recall_at_k(found, truth, 10)
+        gsample = min(index.vectors.size(0), 10_000)
+        gtruth = brute_force_topk(index.vectors, index.vectors[:gsample], 11, w["metric"])[:, 1:]
+        graph_recall = recall_at_k(index.beams[:gsample], gtruth, 10)
     status = _lib.read_status(dev)
 
     times = torch.tensor([ms_total, e2e_ms, search_ms], device=dev, dtype=torch.float64)
@@ -348,7 +370,8 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": name, "vectors_per_gpu": n, "dim": dim, **kw, "loops_run": vl_ann.generate_ann.last_loops,
                        "l2_policy": "inputs (vectors %d MB + graph) exceed the 126 MB L2" % (n * dim * 4 // 2**20),
-                       "sharding": "one independent shard per GPU, no collective in the build step" if world > 1 else "none"},
+                       "sharding": ("vectors all-gathered, each round's rows split across ranks, new neighbour lists "
+                                    "broadcast per round (NCCL)") if world > 1 else "none"},
             "e2e": {"value": world * n / (e2e_ms / args.steps * 1e-3), "unit": "vectors/s",
                     "h2d_bytes_per_step": n * dim * 4, "d2h_bytes_per_step": n * kw["beam_size"] * 8},
             "gpu_launches": launches,

@@ -286,7 +286,15 @@ def excluding_self(start, end, queue_length, device="cuda"):
     return torch.arange(start, end, dtype=torch.int32, device=device).unsqueeze(1).contiguous()
 
 
-def generate_ann(vectors: Tensor, config: Dict) -> Tuple[Tensor, Tensor]:
+def _share_rows(t: Tensor, bounds, group) -> None:
+    """Every rank ends up with every row block of `t`: block s is broadcast by its owner."""
+    import torch.distributed as dist
+    for s, (lo, hi) in enumerate(bounds):
+        if hi > lo:
+            dist.broadcast(t[lo:hi], src=dist.get_global_rank(group, s) if group is not None else s, group=group)
+
+
+def generate_ann(vectors: Tensor, config: Dict, group=None) -> Tuple[Tensor, Tensor]:
     """ann.py:109-193: circulant start graph of width W = beam_size * beam_queue_factor, then up
     to `optimization_loops` rounds of: beam-search every node from its current neighbours
     (batch by batch in the reference; all batches in one launch here, since a batch only
@@ -294,7 +302,11 @@ def generate_ann(vectors: Tensor, config: Dict) -> Tuple[Tensor, Tensor]:
     Departures from the reference, both where its own result is accidental: the distances
     carried into the next round and returned are those of the neighbour lists (the reference
     keeps the initial circulant distances, ann.py:172 assigns to an unused name), and a
-    MAXINT neighbour yields sentinels instead of an out-of-range read."""
+    MAXINT neighbour yields sentinels instead of an out-of-range read.
+
+    With `group` (a torch.distributed group whose ranks all hold the same `vectors`) the rows of
+    each round are split across the ranks in whole batches and the new neighbour lists are
+    exchanged after the search, so every rank ends with the same graph as a single-GPU build."""
     _lib.require_cuda(vectors)
     (num_vecs, vec_dim) = vectors.size()
     beam_size = config["beam_size"]
@@ -309,6 +321,16 @@ def generate_ann(vectors: Tensor, config: Dict) -> Tuple[Tensor, Tensor]:
     capacity = queue_length + remaining_capacity
     batch_size = config["batch_size"]
     fused = not config.get("stepwise", False) and _fused_shape_ok(vectors, queue_length, queue_length, capacity, config)
+    row_lo, row_hi, bounds = 0, num_vecs, None
+    if group is not None:
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world > 1:
+            n_batches = (num_vecs + batch_size - 1) // batch_size
+            from .sharded import partition_rows
+            bounds = [(min(num_vecs, lo * batch_size), min(num_vecs, hi * batch_size))
+                      for lo, hi in partition_rows(n_batches, world)]
+            row_lo, row_hi = bounds[rank]
     loops_run = 0
     for i in range(0, config["optimization_loops"]):
         print_timestamp(f"start of cagra loop {i}")
@@ -316,6 +338,7 @@ def generate_ann(vectors: Tensor, config: Dict) -> Tuple[Tensor, Tensor]:
         next_beam_distances = torch.empty_like(beam_distances)
 
         def batch_stepwise(lo, hi):
+            lo, hi = lo + row_lo, hi + row_lo
             exclude = excluding_self(lo, hi, queue_length, dev)
             queue = Queue(hi - lo, queue_length, capacity, device=dev)
             queue.insert(beams.narrow(0, lo, hi - lo), beam_distances.narrow(0, lo, hi - lo))
@@ -324,12 +347,18 @@ def generate_ann(vectors: Tensor, config: Dict) -> Tuple[Tensor, Tensor]:
             next_beam_distances.narrow(0, lo, hi - lo).copy_(queue.distances.narrow(1, 0, queue_length))
             return n
 
-        if fused:
-            _fused_batches(vectors, beams, vectors, beams, beam_distances, queue_length, queue_length, capacity,
-                           config, None, 0, batch_size, next_beams, next_beam_distances, queue_length, batch_stepwise)
-        else:
-            for lo in range(0, num_vecs, batch_size):
-                batch_stepwise(lo, min(num_vecs, lo + batch_size))
+        if row_hi > row_lo:
+            if fused:
+                _fused_batches(vectors, beams, vectors[row_lo:row_hi], beams[row_lo:row_hi],
+                               beam_distances[row_lo:row_hi], queue_length, queue_length, capacity, config, None,
+                               row_lo, batch_size, next_beams[row_lo:row_hi], next_beam_distances[row_lo:row_hi],
+                               queue_length, batch_stepwise)
+            else:
+                for lo in range(0, row_hi - row_lo, batch_size):
+                    batch_stepwise(lo, min(row_hi - row_lo, lo + batch_size))
+        if bounds is not None:
+            _share_rows(next_beams, bounds, group)
+            _share_rows(next_beam_distances, bounds, group)
 
         if config["prune"]:
             (beams, beam_distances) = prune_(next_beams, next_beam_distances)
@@ -371,7 +400,7 @@ def query_distances(query_vectors: Tensor, vectors: Tensor, ids: Tensor, metric=
     return calculate_distances(vectors, ids, metric=metric, queries=query_vectors)
 
 
-def initial_search_queue(vectors: Tensor, query_vectors: Tensor, config: Dict):
+def initial_search_queue(vectors: Tensor, query_vectors: Tensor, config: Dict, first_row: int = 0):
     """ann.py:217-232: circulant seeds (b + p_j) mod N for query row b; the queue starts as the
     Q = recall_search_queue_factor * beam_size seeds ordered by distance.
     config["search_seed_factor"] (added, default 1 = the reference) scans that many times Q
@@ -384,7 +413,7 @@ def initial_search_queue(vectors: Tensor, query_vectors: Tensor, config: Dict):
     seed_count = queue_size * max(1, int(config.get("search_seed_factor", 1)))
     p = primes(seed_count, vectors.device)
     (vector_count, _) = vectors.size()
-    initial_queue_indices = generate_queue_circulants(batch_size, vector_count, p)
+    initial_queue_indices = generate_queue_circulants(batch_size, vector_count, p, first_row)
     d = query_distances(query_vectors, vectors, initial_queue_indices, _metric_of(config))
     if seed_count <= extra_capacity:
         queue.insert(initial_queue_indices, d)
@@ -432,13 +461,14 @@ class ANN:
     `.distances` fp32 [N, beam_size], `.search(query)` returns the search `Queue`.
     Added keywords: metric ("cosine" - the reference's distance on unit vectors - or "l2") and
     search_seed_factor (how many times Q seeds `.search` scans for its starting queue; 1 = the
-    reference)."""
+    reference) and group (a torch.distributed group whose ranks all pass the same vectors: the
+    build's rows are split across them, see generate_ann)."""
 
     def __init__(self, vectors: Tensor, prune: bool = True, beam_size: int = 24, parallel_visit_count: int = 4,
                  beam_queue_factor: int = 3, visit_queue_factor: int = 3, exclude_factor: int = 5,
                  optimization_loops: int = 3, batch_size: int = 10_000, recall_search_queue_factor: int = 3,
                  speculative_readahead: int = 5, beams: Optional[Tensor] = None, distances: Optional[Tensor] = None,
-                 metric: str = "cosine", search_seed_factor: int = 1):
+                 metric: str = "cosine", search_seed_factor: int = 1, group=None):
         (count, dim) = vectors.size()
         assert vectors.dtype == torch.float32
         _lib.require_cuda(vectors)
@@ -468,7 +498,7 @@ class ANN:
             else:
                 self.distances = distances
         else:
-            (self.beams, self.distances) = generate_ann(self.vectors, self.configuration)
+            (self.beams, self.distances) = generate_ann(self.vectors, self.configuration, group=group)
         torch.cuda.synchronize(self.vectors.device)
         wall_end = time.time()
         total_time: float = wall_end - wall_start
@@ -492,13 +522,15 @@ class ANN:
         closest_vectors(self.vectors, queue, self.vectors, self.beams, self.configuration)
         return queue
 
-    def search(self, query: Tensor) -> Queue:
+    def search(self, query: Tensor, first_row: int = 0) -> Queue:
         """ann.py:469-477: `query` fp32 [B, dim] -> Queue with `.indices` int32 and `.distances`
         fp32 of shape [B, Q + max(Q, pvc*beam_size)], Q = recall_search_queue_factor*beam_size
-        = `.length`; rows ascending by distance, ids unique, MAXINT/MAXFLOAT padding."""
+        = `.length`; rows ascending by distance, ids unique, MAXINT/MAXFLOAT padding.
+        `first_row` (added): index of query row 0 in the batch it was cut from (the seeds of a
+        row depend on its index)."""
         assert query.dtype == torch.float32
         query = query.contiguous()
-        search_queue = initial_search_queue(self.vectors, query, self.configuration)
+        search_queue = initial_search_queue(self.vectors, query, self.configuration, first_row)
         closest_vectors(query, search_queue, self.vectors, self.beams, self.configuration, None)
         return search_queue
 

@@ -4,16 +4,25 @@ reference, which is single-device: `DEVICE = "cuda"`, constants.py:7).
 One process per GPU, `torch.distributed` for the plumbing (NCCL on GPUs).  Rank r owns a
 contiguous block of rows of the vector set; ids stay global int32.
 
-build   1. every rank builds the graph of its own shard with the single-GPU path (no
+Two build modes:
+
+mode="shards"
+        1. every rank builds the graph of its own shard with the single-GPU path (no
            communication);
         2. merge pass, chunk by chunk: the owners' rows are all-gathered, every rank searches
            its local graph for the rows of the other shards (`ANN.search` on the local
            index), the per-shard candidate lists [chunk, D] (global ids, distances) are
            all-gathered, and each owner keeps the D best distinct (distance, id) pairs of its
-           own list and the G-1 foreign ones;
-search  3. vectors and merged graph are all-gathered so that every GPU holds the whole index
-           (20M x 1024 fp32 + a degree-64 graph is 87 GB of a B200's 180 GB), query batches
-           are split across ranks, searched independently and the queues all-gathered.
+           own list and the G-1 foreign ones.  Work per GPU grows with the number of shards
+           (every shard is searched for every foreign row).
+mode="rows" (default)
+        the shards' vectors are all-gathered first (20M x 1024 fp32 is 82 GB of a B200's
+        180 GB), then the single-GPU algorithm runs with the ROWS of every round split across
+        the ranks and the new neighbour lists exchanged after each round (generate_ann with
+        `group`): the graph is the one a single GPU would build over the whole set, and the
+        work per GPU does not depend on the number of ranks.
+search  vectors and graph are on every GPU, query batches are split across the ranks,
+        searched independently and the queues all-gathered.
 
 Remote rows only ever arrive through collectives into this GPU's own memory before a kernel
 reads them.  The choreography is independent of the device: the unit tests run it on CPU
@@ -123,17 +132,26 @@ class ShardedANN:
     (with `replicate=True`) `.index`, an `ANN` over the whole set on every rank for `.search`.
     """
 
-    def __init__(self, local_vectors: Tensor, group=None, merge: bool = True, replicate: bool = True,
-                 chunk_rows: int = 65536, **ann_kwargs):
+    def __init__(self, local_vectors: Tensor, group=None, mode: str = "rows", merge: bool = True,
+                 replicate: bool = True, chunk_rows: int = 65536, **ann_kwargs):
         from .ann import ANN
         from .kernels import sort_pairs_
-        self.group = group
+        assert mode in ("rows", "shards")
+        self.group = group if group is not None else dist.group.WORLD
+        group = self.group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.offsets = shard_offsets(local_vectors.size(0), group)
+        base = self.offsets[self.rank]
+        if mode == "rows":
+            self.local = None
+            vectors = self._gather_blocks(local_vectors.contiguous())
+            self.index = ANN(vectors, group=group if self.world > 1 else None, **ann_kwargs)
+            self.beams = self.index.beams[base:self.offsets[self.rank + 1]]
+            self.distances = self.index.distances[base:self.offsets[self.rank + 1]]
+            return
         self.local = ANN(local_vectors, **ann_kwargs)
         degree = self.local.beams.size(1)
-        base = self.offsets[self.rank]
         ids = torch.where(self.local.beams == MAXINT, self.local.beams, self.local.beams + base)
         dist_ = self.local.distances
 
@@ -154,22 +172,25 @@ class ShardedANN:
         if replicate:
             self.index = self._replicate(ann_kwargs)
 
+    def _gather_blocks(self, t: Tensor) -> Tensor:
+        """Row blocks of every rank (sizes from self.offsets) concatenated in rank order."""
+        sizes = [self.offsets[s + 1] - self.offsets[s] for s in range(self.world)]
+        if self.world == 1:
+            return t
+        pad = max(sizes)
+        buf = torch.zeros((pad,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        buf[: t.size(0)] = t
+        g = _all_gather_rows(buf, self.group)
+        if all(sz == pad for sz in sizes):
+            return g.reshape((-1,) + tuple(t.shape[1:]))
+        return torch.cat([g[s, : sizes[s]] for s in range(self.world)], 0).contiguous()
+
     def _replicate(self, ann_kwargs):
         from .ann import ANN
-        total = self.offsets[-1]
-        sizes = [self.offsets[s + 1] - self.offsets[s] for s in range(self.world)]
-        pad = max(sizes)
-
-        def gather(t: Tensor) -> Tensor:
-            buf = torch.zeros((pad,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-            buf[: t.size(0)] = t
-            g = _all_gather_rows(buf, self.group)
-            return torch.cat([g[s, : sizes[s]] for s in range(self.world)], 0).contiguous()
-
-        vectors = gather(self.local.vectors)
-        beams = gather(self.beams)
-        distances = gather(self.distances)
-        assert vectors.size(0) == total
+        vectors = self._gather_blocks(self.local.vectors)
+        beams = self._gather_blocks(self.beams.contiguous())
+        distances = self._gather_blocks(self.distances.contiguous())
+        assert vectors.size(0) == self.offsets[-1]
         kw = {k: v for k, v in ann_kwargs.items() if k not in ("beams", "distances")}
         kw["beam_size"] = beams.size(1)
         return ANN(vectors, beams=beams, distances=distances, **kw)
@@ -182,7 +203,7 @@ class ShardedANN:
         bounds = split_queries(query.size(0), self.world)
         lo, hi = bounds[self.rank]
         width = max(h - l for l, h in bounds)
-        q = self.index.search(query[lo:hi].contiguous()) if hi > lo else None
+        q = self.index.search(query[lo:hi].contiguous(), first_row=lo) if hi > lo else None
         cap = self.index.search(query[:1].contiguous()).indices.size(1) if q is None else q.indices.size(1)
         ids = torch.full((width, cap), MAXINT, dtype=torch.int32, device=query.device)
         dd = torch.full((width, cap), MAXFLOAT, dtype=torch.float32, device=query.device)

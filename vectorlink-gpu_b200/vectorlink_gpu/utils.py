@@ -32,9 +32,10 @@ def primes(size: int, device="cuda") -> Tensor:
     return ext.to(torch.int32)
 
 
-def generate_queue_circulants(batch_size: int, num_vecs: int, primes: Tensor) -> Tensor:
-    """utils.py:26-32: seeds[b, j] = sort_j(b + p_j) mod num_vecs."""
-    indices = torch.arange(batch_size, device=primes.device, dtype=torch.int32)
+def generate_queue_circulants(batch_size: int, num_vecs: int, primes: Tensor, first_row: int = 0) -> Tensor:
+    """utils.py:26-32: seeds[b, j] = sort_j(b + p_j) mod num_vecs; `first_row` (added) numbers the
+    rows from there, for a batch that is a slice of a larger one."""
+    indices = torch.arange(first_row, first_row + batch_size, device=primes.device, dtype=torch.int32)
     circulant_neighbors = indices.unsqueeze(1) + primes.unsqueeze(0)
     return (circulant_neighbors.sort().values % num_vecs).contiguous()
 
