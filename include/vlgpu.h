@@ -150,7 +150,7 @@ typedef struct vl_beam_params {
     unsigned long long* memo;  /* [memo_slots, memo_entries] scratch, any contents (see vl_beam_search_plan) */
     int64_t memo_slots;        /* rows in flight the scratch was sized for: >= blocks * warps_per_block of the plan */
     unsigned long long* stats; /* optional [16] counters (added to): [1] gathered candidates, [2] search-queue merges,
-                                  [3] visit-queue merges, [6] rows, [7] iterations, [8..13] warp cycles spent in: pop +
+                                  [3] visit-queue merges, [4] class-A candidates, [5] class-B rounds, [6] rows, [7] iterations, [8..13] warp cycles spent in: pop +
                                   neighbour ids, memo probe, gather, memo update, search-queue merge, visit-queue merge */
     int32_t flags;             /* bit 0: also accumulate the per-phase cycle counters of `stats` */
     int32_t reserved;

@@ -192,7 +192,7 @@ __device__ __forceinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int 
 
 // JU > 0: exact-fit rows (dim == 4*LPR*JU, see vl_load_exact); JU == 0: any dim % 4 == 0.
 template <int LPR, int JP, int JU, int METRIC>
-__global__ void __launch_bounds__(kBeamWarps * 32, 5)
+__global__ void __launch_bounds__(kBeamWarps * 32, 4)
 beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -211,7 +211,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
     const int memo_buckets = p.memo ? (p.memo_entries >> 1) : 0;
     int memo_shift = 32;
     for (int b = memo_buckets; b > 1; b >>= 1) --memo_shift;
-    vl_key_t* memo = p.memo ? p.memo + ((size_t)blockIdx.x * (blockDim.x >> 5) + warp) * (size_t)p.memo_entries : nullptr;
+    vl_key_t* const memo_base = p.memo ? p.memo + ((size_t)blockIdx.x * (blockDim.x >> 5) + warp) * (size_t)p.memo_entries : nullptr;
 
     const int wb = p.graph_w, pvc = p.pvc, m_total = p.pvc * p.graph_w;
     const int sq_len = p.sq_len, vq_len = p.vq_len, e_cap = p.seen_cap;
@@ -240,6 +240,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         // ---- prologue: Queue.insert of the seeds into an empty queue (queue.py:37-61) ----
         for (int i = lane; i < sq_len; i += 32) sq[i] = kSent;
         for (int i = lane; i < lay.hash_slots; i += 32) hash[i] = kHashEmpty;
+        vl_key_t* memo = memo_base;
         if (memo) {
             ulonglong2* m2 = reinterpret_cast<ulonglong2*>(memo);
             for (int i = lane; i < memo_buckets; i += 32) m2[i] = make_ulonglong2(~0ull, ~0ull);
@@ -262,8 +263,8 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         __syncwarp();
 
         bool always_full = true;
-        unsigned long long st_todo = 0, st_sm = 0, st_vm = 0, st_iter = 0;
-        long long tk[6] = {0, 0, 0, 0, 0, 0};     // cycles per phase when p.stats is given
+        unsigned long long st_todo = 0, st_sm = 0, st_vm = 0, st_iter = 0, st_a = 0, st_b = 0;
+        long long tk[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};     // cycles per phase when p.stats is given
         const bool timing = p.stats != nullptr && (p.flags & 1);
         long long t_prev = timing ? clock64() : 0;
 #define VL_PHASE(i) do { if (timing) { long long t_now = clock64(); tk[i] += t_now - t_prev; t_prev = t_now; } } while (0)
@@ -346,6 +347,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     n_todo += __popc(mask);
                 }
             }
+
             __syncwarp();
             st_todo += n_todo;
             st_iter += 1;
@@ -468,6 +470,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 #else
                 if (n_old > 0 && vq_len - n_old <= 8) {
 #endif
+                    VL_PHASE(6);
                     const vl_key_t t0key = vq[n_old - 1];
                     int n_a = 0;
                     for (int c0 = 0; c0 < m_total; c0 += 32) {
@@ -478,6 +481,8 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                         n_a += __popc(mask);
                     }
                     __syncwarp();
+                    VL_PHASE(7);
+                    st_a += n_a;
                     vl_key_t vcut = vq[vq_len - 1];
                     for (int t0 = 0; t0 < n_a; t0 += 32) {
                         const int t = t0 + lane;
@@ -489,11 +494,13 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                         st_vm += 1;
                         vcut = vq[vq_len - 1];
                     }
+                    VL_PHASE(8);
                     int n_real = 0;
                     for (int i0 = 0; i0 < vq_len; i0 += 32)
                         n_real += __popc(__ballot_sync(0xffffffffu, i0 + lane < vq_len && vq[i0 + lane] != kSent));
                     vl_key_t last = t0key;
                     while (n_real < vq_len) {
+                        st_b += 1;
                         vl_key_t best = ~0ull;
                         for (int c = lane; c < m_total; c += 32) {
                             const vl_key_t kk = candk[c];
@@ -512,6 +519,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                         st_vm += 1;
                     }
                     __syncwarp();
+                    VL_PHASE(9);
                 } else {
                     // an (almost) empty queue: offer every candidate, 32 at a time
                     vl_key_t vcut = vq[vq_len - 1];
@@ -544,10 +552,12 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             atomicAdd(p.stats + 1, st_todo);
             atomicAdd(p.stats + 2, st_sm);
             atomicAdd(p.stats + 3, st_vm);
+            atomicAdd(p.stats + 4, st_a);
+            atomicAdd(p.stats + 5, st_b);
             atomicAdd(p.stats + 6, 1ull);
             atomicAdd(p.stats + 7, st_iter);
             if (timing)
-                for (int i = 0; i < 6; ++i) atomicAdd(p.stats + 8 + i, (unsigned long long)tk[i]);
+                for (int i = 0; i < 10; ++i) atomicAdd(p.stats + 8 + i, (unsigned long long)tk[i]);
         }
         __syncwarp();
     }
