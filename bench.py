@@ -396,15 +396,14 @@ def main():
             line["cpu_baseline"] = {"value": rate, "unit": "vectors/s", "cores": threads, "kind": "port",
                                     "sample": f"full build of a {sample}-vector draw of {name} ({loops} loops, {dt:.1f} s), "
                                               "C oracle with OpenMP"}
-        traffic_file = os.path.join(ROOT, "profiles", "beam_search_traffic.json")
-        if os.path.exists(traffic_file):
-            try:
-                tr = json.load(open(traffic_file))
-                if big and tr.get("dram_bytes_per_eval"):
-                    line["roofline"]["traffic"] = tr["dram_bytes_per_eval"] * k_evals[big[0]]
-                    line["roofline"]["traffic_note"] = tr.get("note")
-            except Exception:
-                pass
+        # measured DRAM bytes per evaluation of this kernel on this workload (ncu summary in profiles/)
+        traffic_file = os.path.join(ROOT, "profiles", f"beam_search_kernel_{name}_dram_traffic.md")
+        if os.path.exists(traffic_file) and big:
+            import re
+            m = re.search(r"^dram_bytes_per_eval:\s*([0-9.]+)", open(traffic_file).read(), re.M)
+            if m:
+                line["roofline"]["traffic"] = float(m.group(1)) * k_evals[big[0]]
+                line["roofline"]["traffic_source"] = os.path.relpath(traffic_file, ROOT)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
