@@ -184,7 +184,7 @@ def run_reference(args, w, name):
     value = float(np.mean(rates))
     line = {"impl": "reference", "metric": "graph_build_vectors_per_s", "value": value, "unit": "vectors/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": name, "sample_vectors": sample, **{k: v for k, v in ann_kwargs(w).items()}},
             "cpu_baseline": {"value": value, "unit": "vectors/s", "cores": threads, "kind": "port",
                              "sample": f"full build of a {sample}-vector draw of {name} ({loops} loops), C oracle with OpenMP"},
@@ -234,17 +234,21 @@ def main():
     kw = ann_kwargs(w)
     if args.loops:
         kw["optimization_loops"] = args.loops
-    # weak scaling: the job is world x w["n"] vectors; rank r starts with rows [r*n, (r+1)*n) in its
-    # HBM.  A step all-gathers the shards and runs the build with every round's rows split across
-    # the ranks (ShardedANN mode "rows": the graph a single GPU would build over the whole set).
-    n = w["n"]
+    # strong scaling: the job is always the workload's w["n"] vectors; rank r starts with rows
+    # [lo_r, hi_r) of them in its HBM.  A step all-gathers the shards and runs the build with every
+    # round's rows split across the ranks (ShardedANN mode "rows"): the graph is bit-identical to
+    # the one a single GPU builds, whatever the number of ranks.
+    total = w["n"]
+    full, queries = make_data(w, total, dev, seed=0)
     if world > 1:
-        full, queries = make_data(w, n * world, dev, seed=0)
-        vectors = full[rank * n:(rank + 1) * n].clone()
+        from vectorlink_gpu.sharded import partition_rows
+        lo, hi = partition_rows(total, world)[rank]
+        vectors = full[lo:hi].clone()
         del full
         torch.cuda.empty_cache()
     else:
-        vectors, queries = make_data(w, n, dev, seed=0)
+        vectors = full
+    n = vectors.size(0)
     dim = vectors.size(1)
     host_vectors = torch.empty((n, dim), dtype=torch.float32, pin_memory=True)
     host_vectors.copy_(vectors)
@@ -365,17 +369,17 @@ def main():
         peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650"
         ms_per_step = ms_total / args.steps
         line = {
-            "metric": "graph_build_vectors_per_s", "value": world * n / (ms_per_step * 1e-3), "unit": "vectors/s",
+            "metric": "graph_build_vectors_per_s", "value": total / (ms_per_step * 1e-3), "unit": "vectors/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": name, "vectors_per_gpu": n, "dim": dim, **kw, "loops_run": vl_ann.generate_ann.last_loops,
-                       "l2_policy": "inputs (vectors %d MB + graph) exceed the 126 MB L2" % (n * dim * 4 // 2**20),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "vectors": total, "vectors_per_gpu": n, "dim": dim, **kw, "loops_run": vl_ann.generate_ann.last_loops,
+                       "l2_policy": "inputs (vectors %d MB + graph) exceed the 126 MB L2" % (total * dim * 4 // 2**20),
                        "sharding": ("vectors all-gathered, each round's rows split across ranks, new neighbour lists "
                                     "broadcast per round (NCCL)") if world > 1 else "none"},
-            "e2e": {"value": world * n / (e2e_ms / args.steps * 1e-3), "unit": "vectors/s",
-                    "h2d_bytes_per_step": n * dim * 4, "d2h_bytes_per_step": n * kw["beam_size"] * 8},
+            "e2e": {"value": total / (e2e_ms / args.steps * 1e-3), "unit": "vectors/s",
+                    "h2d_bytes_per_step": total * dim * 4, "d2h_bytes_per_step": total * kw["beam_size"] * 8},
             "gpu_launches": launches,
-            "search": {"qps": world * queries.size(0) / (search_ms * 1e-3), "queries": queries.size(0), "k": 10,
+            "search": {"qps": queries.size(0) / (search_ms * 1e-3), "queries": queries.size(0), "k": 10,
                        "recall_at_10": recall, "ms": search_ms,
                        "kernel_gbs": (s_evals * bytes_per_eval / (s_k_ms * 1e-3) / 1e9) if s_k_ms else None},
             "graph_recall_at_10": graph_recall,
