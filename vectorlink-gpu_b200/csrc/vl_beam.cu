@@ -49,7 +49,6 @@ __host__ __device__ inline BeamSmem beam_smem_layout(int m, int sq_len, int vq_l
     s.vq_a = off; off += 8 * vq_len;
     s.vq_b = off; off += 8 * vq_len;
     int slots = 32, shift = 27;
-    #pragma unroll 1
     while (slots < seen_cap + seen_cap / 2 + 1) { slots <<= 1; --shift; }
     s.hash_slots = slots;
     s.hash_shift = shift;
@@ -66,7 +65,7 @@ __device__ __forceinline__ unsigned hash_slot(int32_t id, int shift) { return ((
 __device__ __noinline__ void hash_insert(int32_t* table, int slots, int shift, int32_t id, int* status)
 {
     unsigned s = hash_slot(id, shift);
-    #pragma unroll 1
+#pragma unroll 1
     for (int probe = 0; probe < slots; ++probe) {
         int32_t prev = atomicCAS(&table[s], kHashEmpty, id);
         if (prev == kHashEmpty || prev == id) return;
@@ -78,7 +77,7 @@ __device__ __noinline__ void hash_insert(int32_t* table, int slots, int shift, i
 __device__ __noinline__ bool hash_contains(const int32_t* table, int slots, int shift, int32_t id)
 {
     unsigned s = hash_slot(id, shift);
-    #pragma unroll 1
+#pragma unroll 1
     for (int probe = 0; probe < slots; ++probe) {
         int32_t v = table[s];
         if (v == id) return true;
@@ -137,7 +136,7 @@ __device__ __noinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int len
     int lo = 0;
     if (want) {   // lo = number of list keys below key
         int hi = len;
-        #pragma unroll 1
+#pragma unroll 1
         while (lo < hi) {
             int mid = (lo + hi) >> 1;
             if (cur[mid] < key) lo = mid + 1; else hi = mid;
@@ -150,7 +149,7 @@ __device__ __noinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int len
         const int src = __ffs(wmask) - 1;
         const vl_key_t k0 = __shfl_sync(0xffffffffu, key, src);
         const int pos = __shfl_sync(0xffffffffu, lo, src);
-        #pragma unroll 1
+#pragma unroll 1
         for (int jb = 0; jb < len; jb += 32) {
             const int j = jb + lane;
             if (j < len) {
@@ -172,7 +171,7 @@ __device__ __noinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int len
     lo = 0;
     if (valid) {
         int hi = len;
-        #pragma unroll 1
+#pragma unroll 1
         while (lo < hi) {
             int mid = (lo + hi) >> 1;
             if (cur[mid] < k) lo = mid + 1; else hi = mid;
@@ -184,13 +183,13 @@ __device__ __noinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int len
     if (valid) mpos[rank] = lo;
     __syncwarp();
     // a list element moves down by the number of entering keys below it (those with pos <= j)
-    #pragma unroll 1
+#pragma unroll 1
     for (int jb = 0; jb < len; jb += 32) {
         const int j = jb + lane;
         if (j < len) {
             const vl_key_t e = cur[j];
             int shift = 0;
-            #pragma unroll 1
+#pragma unroll 1
             for (int s = 0; s < nv; ++s) shift += (mpos[s] <= j);
             if (j + shift < len) nxt[j + shift] = e;
         }
@@ -221,7 +220,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
     // 2-entry buckets; ~0 = empty.  Only this warp touches its slice.
     const int memo_buckets = p.memo ? (p.memo_entries >> 1) : 0;
     int memo_shift = 32;
-    #pragma unroll 1
+#pragma unroll 1
     for (int b = memo_buckets; b > 1; b >>= 1) --memo_shift;
     vl_key_t* const memo_base = p.memo ? p.memo + ((size_t)blockIdx.x * (blockDim.x >> 5) + warp) * (size_t)p.memo_entries : nullptr;
 
@@ -238,7 +237,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
     const int wpb = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * wpb + warp;
     const int64_t nwarps = (int64_t)gridDim.x * wpb;
-    #pragma unroll 1
+#pragma unroll 1
     for (int64_t row = warp0; row < p.rows; row += nwarps) {
         vl_key_t* sq = reinterpret_cast<vl_key_t*>(base + lay.sq_a);
         vl_key_t* sq_n = reinterpret_cast<vl_key_t*>(base + lay.sq_b);
@@ -251,18 +250,18 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         else vl_load_query<LPR, JP, true>(q, p.dim, lg, qr);
 
         // ---- prologue: Queue.insert of the seeds into an empty queue (queue.py:37-61) ----
-        #pragma unroll 1
+#pragma unroll 1
         for (int i = lane; i < sq_len; i += 32) sq[i] = kSent;
-        #pragma unroll 1
+#pragma unroll 1
         for (int i = lane; i < lay.hash_slots; i += 32) hash[i] = kHashEmpty;
         vl_key_t* memo = memo_base;
         if (memo) {
             ulonglong2* m2 = reinterpret_cast<ulonglong2*>(memo);
-            #pragma unroll 1
+#pragma unroll 1
             for (int i = lane; i < memo_buckets; i += 32) m2[i] = make_ulonglong2(~0ull, ~0ull);
         }
         __syncwarp();
-        #pragma unroll 1
+#pragma unroll 1
         for (int c0 = 0; c0 < p.seed_cols; c0 += 32) {
             int c = c0 + lane;
             vl_key_t key = kSent;
@@ -275,7 +274,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         // visit_queue.initialize_from_queue (queue.py:30-35)
         {
             const int head = sq_len < vq_len ? sq_len : vq_len;
-            #pragma unroll 1
+#pragma unroll 1
             for (int i = lane; i < vq_len; i += 32) vq[i] = i < head ? sq[i] : kSent;
         }
         __syncwarp();
@@ -291,7 +290,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         const int64_t group = p.group_rows > 0 ? row / p.group_rows : 0;
         bool dumped = false;
 
-        #pragma unroll 1
+#pragma unroll 1
         for (int k = 1; k <= n_run; ++k) {
             const int first = (k - 1) * pvc;
             const bool seen_live = first < e_cap;    // utils.py:62-69
@@ -316,7 +315,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                         else if ((uint32_t)e1 == (uint32_t)node) bk[1] = kPopped | (uint32_t)node;
                     }
                 }
-                #pragma unroll 1
+#pragma unroll 1
                 for (int i = lane; i < vq_len; i += 32) vq_n[i] = (i + pvc < vq_len) ? vq[i + pvc] : kSent;
                 __syncwarp();
                 vl_key_t* t = vq; vq = vq_n; vq_n = t;
@@ -327,7 +326,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             // that the graph-row loads, and then the memo loads, of a round are in flight together.
             int n_todo = 0;
             const bool raw_iteration = p.dump_last && k == p.n_iters;   // needs every real distance
-            #pragma unroll 1
+#pragma unroll 1
             for (int cb = 0; cb < m_total; cb += 128) {
                 int32_t idr[4];
 #pragma unroll
@@ -411,25 +410,25 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             __syncwarp();
             VL_PHASE(2);   // gather
             if (memo) {   // remember what was just computed
-                #pragma unroll 1
+#pragma unroll 1
                 for (int t = lane; t < n_todo; t += 32) memo_put(memo, memo_buckets, memo_shift, candk[todo[t]], k & 1);
                 __syncwarp();
             }
             // ---- search_queue.insert(..., exclude) (ann.py:75-80) ----
             if (p.dump_last && k == p.n_iters) {
                 // leave this insert to the caller's full-row sort: head, then the raw candidates
-                #pragma unroll 1
+#pragma unroll 1
                 for (int i = lane; i < sq_len; i += 32) {
                     p.out_ids[row * p.out_ld + i] = vl_key_id(sq[i]);
                     p.out_dist[row * p.out_ld + i] = vl_key_dist(sq[i]);
                 }
-                #pragma unroll 1
+#pragma unroll 1
                 for (int i = lane; i < m_total; i += 32) {
                     vl_key_t key = candk[i];
                     int32_t id = vl_key_id(key);
                     bool drop = (id == self_id);
                     if (!drop && excl)
-                        #pragma unroll 1
+#pragma unroll 1
                         for (int t = 0; t < p.exclude_w; ++t) {
                             int32_t x = excl[t];
                             if (x == VL_MAXINT) break;
@@ -439,7 +438,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     p.out_ids[row * p.out_ld + sq_len + i] = vl_key_id(key);
                     p.out_dist[row * p.out_ld + sq_len + i] = vl_key_dist(key);
                 }
-                #pragma unroll 1
+#pragma unroll 1
                 for (int i = sq_len + m_total + lane; i < p.out_cols; i += 32) {
                     p.out_ids[row * p.out_ld + i] = VL_MAXINT;
                     p.out_dist[row * p.out_ld + i] = VL_MAXFLOAT;
@@ -453,7 +452,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             // offering it again can neither add nor move anything.
             bool changed = false;
             vl_key_t cut = sq[sq_len - 1];
-            #pragma unroll 1
+#pragma unroll 1
             for (int t0 = 0; t0 < n_todo; t0 += 32) {
                 const int t = t0 + lane;
                 vl_key_t key = t < n_todo ? candk[todo[t]] : kSent;
@@ -463,7 +462,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     int32_t id = vl_key_id(key);
                     if (id == self_id) want = false;
                     else if (excl)
-                        #pragma unroll 1
+#pragma unroll 1
                         for (int x = 0; x < p.exclude_w; ++x) {   // kernels.py:478-488
                             int32_t ex = excl[x];
                             if (ex == VL_MAXINT) break;
@@ -492,18 +491,14 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 // above T0 (class B, appended one by one in rising order).  Same queue as offering
                 // every candidate, without sorting the many that are already in it.
                 int n_old = 0;
-                #pragma unroll 1
+#pragma unroll 1
                 for (int i0 = 0; i0 < vq_len; i0 += 32)
                     n_old += __popc(__ballot_sync(0xffffffffu, i0 + lane < vq_len && vq[i0 + lane] != kSent));
-#ifdef VL_OLD_VISIT
-                if (false) {
-#else
                 if (n_old > 0 && vq_len - n_old <= 8) {
-#endif
                     VL_PHASE(6);
                     const vl_key_t t0key = vq[n_old - 1];
                     int n_a = 0;
-                    #pragma unroll 1
+#pragma unroll 1
                     for (int c0 = 0; c0 < m_total; c0 += 32) {
                         const int c = c0 + lane;
                         const bool in_a = c < m_total && candk[c] < t0key;
@@ -515,7 +510,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     VL_PHASE(7);
                     st_a += n_a;
                     vl_key_t vcut = vq[vq_len - 1];
-                    #pragma unroll 1
+#pragma unroll 1
                     for (int t0 = 0; t0 < n_a; t0 += 32) {
                         const int t = t0 + lane;
                         vl_key_t key = t < n_a ? candk[todo[t]] : kSent;
@@ -528,15 +523,15 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     }
                     VL_PHASE(8);
                     int n_real = 0;
-                    #pragma unroll 1
+#pragma unroll 1
                     for (int i0 = 0; i0 < vq_len; i0 += 32)
                         n_real += __popc(__ballot_sync(0xffffffffu, i0 + lane < vq_len && vq[i0 + lane] != kSent));
                     vl_key_t last = t0key;
-                    #pragma unroll 1
+#pragma unroll 1
                     while (n_real < vq_len) {
                         st_b += 1;
                         vl_key_t best = ~0ull;
-                        #pragma unroll 1
+#pragma unroll 1
                         for (int c = lane; c < m_total; c += 32) {
                             const vl_key_t kk = candk[c];
                             if (kk > last && kk < kSent && kk < best) best = kk;
@@ -558,7 +553,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 } else {
                     // an (almost) empty queue: offer every candidate, 32 at a time
                     vl_key_t vcut = vq[vq_len - 1];
-                    #pragma unroll 1
+#pragma unroll 1
                     for (int c0 = 0; c0 < m_total; c0 += 32) {
                         const int c = c0 + lane;
                         vl_key_t key = c < m_total ? candk[c] : kSent;
@@ -577,7 +572,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 
         VL_PHASE(5);       // visit-queue merge of the last iteration + epilogue
         if (!dumped) {
-            #pragma unroll 1
+#pragma unroll 1
             for (int i = lane; i < p.out_cols; i += 32) {
                 vl_key_t key = i < sq_len ? sq[i] : kSent;
                 p.out_ids[row * p.out_ld + i] = vl_key_id(key);
@@ -594,7 +589,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             atomicAdd(p.stats + 6, 1ull);
             atomicAdd(p.stats + 7, st_iter);
             if (timing)
-                #pragma unroll 1
+#pragma unroll 1
                 for (int i = 0; i < 10; ++i) atomicAdd(p.stats + 8 + i, (unsigned long long)tk[i]);
         }
         __syncwarp();
@@ -614,7 +609,6 @@ int plan_and_launch(const vl_beam_params& p, BeamPlan& plan, bool launch, cudaSt
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     VL_CHECK_ARG(e == cudaSuccess, "vl_beam_search: %s", cudaGetErrorString(e));
     plan.warps = kBeamWarps;
-    #pragma unroll 1
     while (plan.warps > 1 && (size_t)plan.warps * plan.lay.total > (size_t)max_smem) plan.warps >>= 1;
     plan.smem = (size_t)plan.warps * plan.lay.total;
     VL_CHECK_ARG(plan.smem <= (size_t)max_smem, "vl_beam_search: one row needs %d bytes of shared memory, the device offers %d",

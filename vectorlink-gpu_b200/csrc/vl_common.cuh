@@ -172,12 +172,6 @@ __device__ __forceinline__ vl_f2 vl_f2_term(float ax, float ay, float bx, float 
 template <int LPR, int JP, int JU, int METRIC>
 __device__ __forceinline__ float vl_exact_distance(const float4 (&xr)[JU], const float4 (&qr)[JU])
 {
-#ifdef VL_NO_F2
-    float4 acc[JP];
-#pragma unroll
-    for (int j = 0; j < JP; ++j) acc[j] = j < JU ? vl_term4<METRIC>(xr[j < JU ? j : 0], qr[j < JU ? j : 0]) : make_float4(0.f, 0.f, 0.f, 0.f);
-    return vl_finish<METRIC>(vl_tree_reduce<LPR, JP, JU>(acc));
-#endif
     vl_f2 axy[JU], azw[JU];
 #pragma unroll
     for (int j = 0; j < JU; ++j) {
