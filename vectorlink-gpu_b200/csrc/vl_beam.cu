@@ -35,11 +35,11 @@ constexpr int kBeamWarps = 4;             // most warps (= rows in flight) per C
 constexpr int32_t kHashEmpty = -1;
 
 struct BeamSmem {      // per-warp carve-up, in bytes from the warp's base
-    int cand, sq_a, sq_b, vq_a, vq_b, hash, pop, mpos, todo, total;
+    int cand, sq_a, sq_b, vq_a, vq_b, hash, pop, mpos, todo, query, total;
     int hash_slots, hash_shift;
 };
 
-__host__ __device__ inline BeamSmem beam_smem_layout(int m, int sq_len, int vq_len, int seen_cap)
+__host__ __device__ inline BeamSmem beam_smem_layout(int m, int sq_len, int vq_len, int seen_cap, int query_bytes)
 {
     BeamSmem s;
     int off = 0;
@@ -56,6 +56,8 @@ __host__ __device__ inline BeamSmem beam_smem_layout(int m, int sq_len, int vq_l
     s.pop = off; off += 4 * 32;
     s.mpos = off; off += 4 * 32;
     s.todo = off; off += 2 * m;
+    off = (off + 15) & ~15;
+    s.query = off; off += query_bytes;
     s.total = (off + 15) & ~15;
     return s;
 }
@@ -244,9 +246,19 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
         vl_key_t* vq = reinterpret_cast<vl_key_t*>(base + lay.vq_a);
         vl_key_t* vq_n = reinterpret_cast<vl_key_t*>(base + lay.vq_b);
         const float* q = p.queries + row * (int64_t)p.dim;
-        constexpr int JQ = JU > 0 ? JU : JP;
+        // Rows of 8 chunks per lane keep the query in shared memory (read back per step: 8
+        // conflict-free 16-byte loads) so that the registers hold two steps of candidate rows;
+        // shorter rows keep it in registers.
+        constexpr bool QSMEM = (JU >= 8);
+        constexpr int JQ = QSMEM ? 1 : (JU > 0 ? JU : JP);
         float4 qr[JQ];
-        if constexpr (JU > 0) vl_load_exact<LPR, JU>(q, lg, qr);
+        const float4* qs = reinterpret_cast<const float4*>(base + lay.query);
+        if constexpr (QSMEM) {
+            float4* qw = reinterpret_cast<float4*>(base + lay.query);
+#pragma unroll 1
+            for (int c = lane; c < p.dim / 4; c += 32) qw[c] = __ldg(reinterpret_cast<const float4*>(q) + c);
+            qr[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else if constexpr (JU > 0) vl_load_exact<LPR, JU>(q, lg, qr);
         else vl_load_query<LPR, JP, true>(q, p.dim, lg, qr);
 
         // ---- prologue: Queue.insert of the seeds into an empty queue (queue.py:37-61) ----
@@ -373,7 +385,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             st_iter += 1;
             VL_PHASE(1);   // neighbour ids + memo probe
             // ---- gathered distances (kernels.py:248-257): G rows per step, U steps in flight ----
-            constexpr int U = (JQ <= 4) ? 2 : 1;
+            constexpr int U = (QSMEM || JQ <= 4) ? 2 : 1;
 #pragma unroll 1
             for (int t0 = 0; t0 < n_todo; t0 += U * G) {
                 bool live[U];
@@ -393,7 +405,10 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 #pragma unroll
                     for (int u = 0; u < U; ++u) vl_load_exact<LPR, JU>(rp[u], lg, x[u]);
 #pragma unroll
-                    for (int u = 0; u < U; ++u) dd[u] = vl_exact_distance<LPR, JP, JU, METRIC>(x[u], qr);
+                    for (int u = 0; u < U; ++u) {
+                        if constexpr (QSMEM) dd[u] = vl_exact_distance_q<LPR, JP, JU, METRIC>(x[u], qs + lg);
+                        else dd[u] = vl_exact_distance<LPR, JP, JU, METRIC>(x[u], qr);
+                    }
                 } else {
                     float4 x[U][JP];
 #pragma unroll
@@ -602,7 +617,7 @@ template <int LPR, int JP, int JU, int METRIC>
 int plan_and_launch(const vl_beam_params& p, BeamPlan& plan, bool launch, cudaStream_t stream)
 {
     auto kernel = beam_search_kernel<LPR, JP, JU, METRIC>;
-    plan.lay = beam_smem_layout(p.pvc * p.graph_w, p.sq_len, p.vq_len, p.seen_cap);
+    plan.lay = beam_smem_layout(p.pvc * p.graph_w, p.sq_len, p.vq_len, p.seen_cap, (JU >= 8) ? p.dim * 4 : 0);
     int dev = 0, sms = 0, max_smem = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -654,7 +669,7 @@ int beam_dispatch(const vl_beam_params* pp, BeamPlan& plan, bool launch, cudaStr
     VL_CHECK_ARG(p.pvc * (int64_t)p.graph_w <= 65535, "vl_beam_search: %d candidates per iteration exceed 65535", p.pvc * p.graph_w);
     VL_CHECK_ARG(!p.memo || (p.memo_entries >= 2 && (p.memo_entries & (p.memo_entries - 1)) == 0 && (uintptr_t)p.memo % 16 == 0),
                  "vl_beam_search: memo_entries must be a power of two >= 2 and the memo 16-byte aligned");
-    if (p.rows == 0) { plan.blocks = 0; plan.warps = kBeamWarps; plan.lay = beam_smem_layout(p.pvc * p.graph_w, p.sq_len, p.vq_len, p.seen_cap); return 0; }
+    if (p.rows == 0) { plan.blocks = 0; plan.warps = kBeamWarps; plan.lay = beam_smem_layout(p.pvc * p.graph_w, p.sq_len, p.vq_len, p.seen_cap, 0); return 0; }
     VlShape shape = vl_pick_shape(p.dim);
     int rc = 0;
     const int chunks = p.dim / 4;

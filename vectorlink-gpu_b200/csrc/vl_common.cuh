@@ -198,6 +198,37 @@ __device__ __forceinline__ float vl_exact_distance(const float4 (&xr)[JU], const
     return vl_finish<METRIC>(__fadd_rn(lo, hi));
 }
 
+// The same with the query read from memory (shared): q4[LPR*j] is the lane's j-th query chunk.
+template <int LPR, int JP, int JU, int METRIC>
+__device__ __forceinline__ float vl_exact_distance_q(const float4 (&xr)[JU], const float4* q4)
+{
+    vl_f2 axy[JU], azw[JU];
+#pragma unroll
+    for (int j = 0; j < JU; ++j) {
+        const float4 qv = q4[LPR * j];
+        axy[j] = vl_f2_term<METRIC>(xr[j].x, xr[j].y, qv.x, qv.y);
+        azw[j] = vl_f2_term<METRIC>(xr[j].z, xr[j].w, qv.z, qv.w);
+    }
+#pragma unroll
+    for (int h = JP / 2; h >= 1; h >>= 1) {
+#pragma unroll
+        for (int j = 0; j < h; ++j)
+            if (j + h < JU) {
+                axy[j] = vl_f2_add(axy[j], axy[j + h]);
+                azw[j] = vl_f2_add(azw[j], azw[j + h]);
+            }
+    }
+    vl_f2 xy = axy[0], zw = azw[0];
+#pragma unroll
+    for (int off = LPR / 2; off >= 1; off >>= 1) {
+        xy = vl_f2_add(xy, __shfl_down_sync(0xffffffffu, xy, off, LPR));
+        zw = vl_f2_add(zw, __shfl_down_sync(0xffffffffu, zw, off, LPR));
+    }
+    float lo, hi;
+    vl_f2_unpack(vl_f2_add(xy, zw), lo, hi);
+    return vl_finish<METRIC>(__fadd_rn(lo, hi));
+}
+
 // The query-side registers of one lane: chunks lg + LPR*j of the first 1024 elements.
 template <int LPR, int JP, bool ALIGNED>
 __device__ __forceinline__ void vl_load_query(const float* __restrict__ q, int dim, int lg, float4 (&qr)[JP])
