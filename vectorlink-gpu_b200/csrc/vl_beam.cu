@@ -336,13 +336,14 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             // ---- neighbour ids of the popped nodes (kernels.py:244), then which of them need a
             // gather: live ids the memo does not know.  Four chunks of 32 candidates per round so
             // that the graph-row loads, and then the memo loads, of a round are in flight together.
+            constexpr int PB = 6;   // chunks of 32 candidates per round of loads
             int n_todo = 0;
             const bool raw_iteration = p.dump_last && k == p.n_iters;   // needs every real distance
 #pragma unroll 1
-            for (int cb = 0; cb < m_total; cb += 128) {
-                int32_t idr[4];
+            for (int cb = 0; cb < m_total; cb += 32 * PB) {
+                int32_t idr[PB];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < PB; ++u) {
                     const int c = cb + 32 * u + lane;
                     idr[u] = VL_MAXINT;
                     if (c < m_total) {
@@ -351,9 +352,9 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                         if (node != VL_MAXINT) idr[u] = __ldg(p.graph + (int64_t)node * wb + (c - v * wb));
                     }
                 }
-                ulonglong2 bk[4];
+                ulonglong2 bk[PB];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < PB; ++u) {
                     if (idr[u] != VL_MAXINT && (idr[u] < 0 || (int64_t)idr[u] >= p.n)) {
                         atomicOr(p.status, VL_STATUS_BAD_ID);
                         idr[u] = VL_MAXINT;
@@ -363,7 +364,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                         bk[u] = *reinterpret_cast<const ulonglong2*>(memo + 2 * (size_t)memo_bucket((uint32_t)idr[u], memo_shift, memo_buckets));
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < PB; ++u) {
                     const int c = cb + 32 * u + lane;
                     const uint32_t id = (uint32_t)idr[u];
                     bool need = (idr[u] != VL_MAXINT);
