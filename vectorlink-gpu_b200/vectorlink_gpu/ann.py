@@ -46,7 +46,7 @@ def _fused_shape_ok(vectors: Tensor, beam_w: int, sq_len: int, sq_cap: int, conf
     vq_len = config["visit_queue_factor"] * config["beam_size"]
     m = pvc * beam_w
     e = config["exclude_factor"] * vq_len
-    smem = 8 * m + 16 * sq_len + 16 * vq_len + 4 * 4 * max(e, 16) + 512
+    smem = 10 * m + 16 * sq_len + 16 * vq_len + 4 * 6 * max(e, 16) + 4 * vectors.size(1) + 512
     return (vectors.size(1) % 4 == 0 and vectors.data_ptr() % 16 == 0 and 1 <= pvc <= 32 and pvc <= vq_len
             and sq_cap == sq_len + m and sq_len <= 4096 and smem <= FUSED_MAX_SMEM_PER_ROW
             and config["speculative_readahead"] >= 1)
