@@ -108,6 +108,14 @@ int vl_seen_add_noalloc(int32_t* seen, int64_t b, int e, const int32_t* visit, i
 int vl_prune(const int32_t* beams, const float* dist, int64_t n, int w, int do_punch, int32_t* beams_out,
              float* dist_out, int out_cols, int* status, void* stream);
 
+/* Reverse edges (the reference only sketches them: symmetrize_beams, kernels.py:503-550, is dead
+ * code): out[y, 0..keep) = the nodes x that list y among the first `scan` columns of beams [n, d],
+ * ordered by (rank of y in x's list, x), MAXINT-padded.  Two calls: phase 0 adds every node's
+ * in-degree to deg [n] (zeroed by the caller); the caller turns deg into exclusive prefix sums
+ * `offsets` [n] (int64) and provides a zeroed cursor [n] and keys [sum(deg)]; phase 1 fills and selects. */
+int vl_reverse_edges(const int32_t* beams, int64_t n, int d, int scan, int phase, int32_t* deg, const int64_t* offsets,
+                     int32_t* cursor, unsigned long long* keys, int keep, int32_t* out, int* status, void* stream);
+
 /* closest_vectors (ann.py:37-93) as one kernel: the whole budgeted beam search of every query
  * row, with the search queue, the visit queue and the visited set of a row held on chip by
  * one warp.  Replaces, per iteration, pop_n_ids + search_from_seeds + two Queue.insert +

@@ -190,3 +190,44 @@ def test_circulants_vs_reference_host_code(c1, built_lib):
     from vectorlink_gpu.utils import generate_circulant_beams, generate_queue_circulants, primes
     assert np.array_equal(n(generate_circulant_beams(50, primes(9, DEV))), c1["op_circ_beams"])
     assert np.array_equal(n(generate_queue_circulants(7, 50, primes(9, DEV))), c1["op_circ_queue"])
+
+
+def test_reverse_edges_vs_numpy(built_lib):
+    from vectorlink_gpu.kernels import reverse_edges
+    rng = np.random.default_rng(8)
+    nn, d, scan, keep = 300, 12, 8, 5
+    beams = rng.integers(0, nn, (nn, d)).astype(np.int32)
+    beams[rng.random((nn, d)) < 0.1] = MAXINT
+    got = n(reverse_edges(t(beams), scan=scan, keep=keep))
+    want = np.full((nn, keep), MAXINT, dtype=np.int32)
+    lists = [[] for _ in range(nn)]
+    for r in range(scan):                       # rank-major, source ascending
+        for x in range(nn):
+            y = beams[x, r]
+            if y != MAXINT:
+                lists[y].append(x)
+    for y in range(nn):
+        row = lists[y][:keep]
+        want[y, :len(row)] = row
+    assert np.array_equal(got, want)
+
+
+def test_symmetrize_adds_reverse_edges_and_keeps_rows_well_formed(built_lib):
+    from vectorlink_gpu.kernels import symmetrize, calculate_distances
+    rng = np.random.default_rng(9)
+    v = unit(rng, 800, 16)
+    kn = oracle.bruteforce_knn(v, v, 12, exclude_self=True)
+    d = oracle.calculate_distances(v, kn)
+    ids, dist = symmetrize(t(v), t(kn), t(d))
+    ids, dist = n(ids), n(dist)
+    assert ids.shape == kn.shape
+    assert np.all(np.diff(dist, axis=1) >= 0)
+    for r in range(800):
+        real = ids[r][ids[r] != MAXINT]
+        assert len(set(real)) == len(real) and r not in real
+    assert np.array_equal(n(calculate_distances(t(v), t(ids))), dist)
+    # the best half of the forward edges survives; reverse edges made it in where they exist
+    assert all(set(kn[r, :6]) <= set(ids[r]) for r in range(800))
+    fwd = [set(row) for row in kn]
+    gained = sum(1 for x in range(800) for y in ids[x] if y != MAXINT and y not in fwd[x] and x in fwd[y])
+    assert gained > 0

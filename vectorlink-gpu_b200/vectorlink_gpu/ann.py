@@ -468,14 +468,14 @@ class ANN:
     `.distances` fp32 [N, beam_size], `.search(query)` returns the search `Queue`.
     Added keywords: metric ("cosine" - the reference's distance on unit vectors - or "l2") and
     search_seed_factor (how many times Q seeds `.search` scans for its starting queue; 1 = the
-    reference) and group (a torch.distributed group whose ranks all pass the same vectors: the
+    reference), symmetrize (add reverse edges after the build; off = the reference) and group (a torch.distributed group whose ranks all pass the same vectors: the
     build's rows are split across them, see generate_ann)."""
 
     def __init__(self, vectors: Tensor, prune: bool = True, beam_size: int = 24, parallel_visit_count: int = 4,
                  beam_queue_factor: int = 3, visit_queue_factor: int = 3, exclude_factor: int = 5,
                  optimization_loops: int = 3, batch_size: int = 10_000, recall_search_queue_factor: int = 3,
                  speculative_readahead: int = 5, beams: Optional[Tensor] = None, distances: Optional[Tensor] = None,
-                 metric: str = "cosine", search_seed_factor: int = 1, group=None):
+                 metric: str = "cosine", search_seed_factor: int = 1, group=None, symmetrize: bool = False):
         (count, dim) = vectors.size()
         assert vectors.dtype == torch.float32
         _lib.require_cuda(vectors)
@@ -506,6 +506,10 @@ class ANN:
                 self.distances = distances
         else:
             (self.beams, self.distances) = generate_ann(self.vectors, self.configuration, group=group)
+        if symmetrize:
+            from .kernels import symmetrize as _symmetrize
+            (self.beams, self.distances) = _symmetrize(self.vectors, self.beams.contiguous(), self.distances.contiguous(),
+                                                       metric=metric)
         torch.cuda.synchronize(self.vectors.device)
         wall_end = time.time()
         total_time: float = wall_end - wall_start
@@ -513,6 +517,46 @@ class ANN:
         self.log["total_time"] = total_time
         self.log["vector_count"] = count
         self.log["vector_dimension"] = dim
+
+    @classmethod
+    def load_from_dataframe(cls, dataframe, device="cuda", **kwargs) -> "ANN":
+        """ann.py:408-454: a saved index back from Arrow data with the columns `vector_id`,
+        `embedding`, `beams` and optionally `distances`.  Takes a `pyarrow.Table` (or a DataFusion
+        DataFrame where that package is installed); rows are ordered by `vector_id`."""
+        import pyarrow as pa
+        import pyarrow.compute as pc
+        from .datafusion import dataframe_to_tensor
+        table = dataframe if isinstance(dataframe, pa.Table) else dataframe.to_arrow_table()
+        names = table.schema.names
+        assert "embedding" in names and "beams" in names
+        if "vector_id" in names:
+            table = table.take(pc.sort_indices(table, sort_keys=[("vector_id", "ascending")]))
+        count = table.num_rows
+
+        def width(name):
+            ty = table.schema.field(name).type
+            size = getattr(ty, "list_size", None)
+            return size if size is not None else len(table.column(name)[0])
+
+        vectors_tensor = torch.empty((count, width("embedding")), dtype=torch.float32, device=device)
+        dataframe_to_tensor(table.column("embedding"), vectors_tensor)
+        beam_size = width("beams")
+        beams_tensor = torch.empty((count, beam_size), dtype=torch.int32, device=device)
+        dataframe_to_tensor(table.column("beams"), beams_tensor)
+        distances_tensor = None
+        if "distances" in names:
+            distances_tensor = torch.empty((count, beam_size), dtype=torch.float32, device=device)
+            dataframe_to_tensor(table.column("distances"), distances_tensor)
+        return ANN(vectors_tensor, beam_size=beam_size, beams=beams_tensor, distances=distances_tensor, **kwargs)
+
+    def to_arrow(self):
+        """The index as a `pyarrow.Table` in the column layout `load_from_dataframe` reads."""
+        import pyarrow as pa
+        from .datafusion import tensor_to_arrow
+        count = self.vectors.size(0)
+        return pa.table({"vector_id": pa.array(range(count), type=pa.int32()),
+                         "embedding": tensor_to_arrow(self.vectors), "beams": tensor_to_arrow(self.beams),
+                         "distances": tensor_to_arrow(self.distances)})
 
     def recall(self, sample_size: int = 1000) -> Tuple[float, float]:
         """ann.py:456-464."""

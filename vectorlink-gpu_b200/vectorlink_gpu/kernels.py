@@ -165,3 +165,65 @@ def sort_pairs_(ids: Tensor, distances: Tensor, dedup: bool):
 def index_by_tensor(a: Tensor, b: Tensor):
     """kernels.py:554-559: row-wise gather a[i, b[i, j]]."""
     return torch.gather(a, 1, b.long())
+
+
+def reverse_edges(beams: Tensor, scan: Optional[int] = None, keep: Optional[int] = None) -> Tensor:
+    """For every node the nodes that list it among their first `scan` neighbours, ordered by
+    (rank in the lister's row, lister id), int32 [N, keep] padded with MAXINT.  The role of the
+    reference's symmetrize_beams (kernels.py:534-550, dead code there)."""
+    assert beams.dtype == torch.int32 and beams.is_contiguous()
+    _lib.require_cuda(beams)
+    (n, d) = beams.size()
+    scan = d if scan is None else scan
+    keep = max(1, d // 2) if keep is None else keep
+    dev = beams.device
+    deg = torch.zeros(n, dtype=torch.int32, device=dev)
+    status = _lib.status_word(dev)
+    check(lib().vl_reverse_edges(ptr(beams), n, d, scan, 0, ptr(deg), None, None, None, keep, None, ptr(status),
+                                 stream_of(beams)), "vl_reverse_edges")
+    offsets = torch.cumsum(deg, 0, dtype=torch.int64) - deg
+    total = int(offsets[-1].item() + deg[-1].item()) if n else 0
+    keys = torch.empty(max(total, 1), dtype=torch.int64, device=dev)
+    cursor = torch.zeros(n, dtype=torch.int32, device=dev)
+    out = torch.empty((n, keep), dtype=torch.int32, device=dev)
+    check(lib().vl_reverse_edges(ptr(beams), n, d, scan, 1, ptr(deg), ptr(offsets), ptr(cursor), ptr(keys), keep,
+                                 ptr(out), ptr(status), stream_of(beams)), "vl_reverse_edges")
+    _lib.LAUNCHES += 1      # the second phase is two kernels (fill, select)
+    return out
+
+
+def symmetrize(vectors: Tensor, beams: Tensor, distances: Tensor, keep: Optional[int] = None, metric="cosine"):
+    """The intent of the reference's `symmetrize` sketch (utils.py:92-103, dead code): give every
+    node up to `keep` (default half its degree) of its reverse edges.  The new row is the
+    distinct ids of: the best degree-keep forward neighbours, then the reverse neighbours, then
+    the remaining forward ones - cut to the degree and ordered by distance.  Not in the
+    reference's live code, so there is no parity target; it is judged by recall."""
+    (n, d) = beams.size()
+    keep = max(1, d // 2) if keep is None else min(keep, d)
+    rev = reverse_edges(beams, scan=d, keep=keep)
+    rev_dist = calculate_distances(vectors, rev, metric=metric)
+    own = torch.arange(n, device=beams.device, dtype=torch.int32).unsqueeze(1)
+    rev = torch.where(rev == own, torch.full_like(rev, MAXINT), rev)
+    # priority classes through a distance bias that is removed after the cut: 0 forward head,
+    # 1 reverse, 2 forward tail; duplicates keep their best class because equal ids are punched
+    # after a sort by (class, distance, id)
+    ids = torch.cat([beams[:, : d - keep], rev, beams[:, d - keep:]], 1).contiguous()
+    dist = torch.cat([distances[:, : d - keep], rev_dist, distances[:, d - keep:]], 1).contiguous()
+    cls = torch.cat([torch.zeros((n, d - keep)), torch.ones((n, keep)), torch.full((n, keep), 2.0)], 1).to(dist.device)
+    cls = torch.where(ids == MAXINT, torch.full_like(cls, 3.0), cls)
+    order = torch.argsort(cls * 4 + (ids.float() / 2 ** 31), dim=1, stable=True)      # class, then id: first copy wins
+    ids, dist, cls = (torch.gather(t, 1, order) for t in (ids, dist, cls))
+    # drop repeated ids keeping the first (best class) occurrence
+    by_id = torch.argsort(ids, dim=1, stable=True)
+    sid = torch.gather(ids, 1, by_id)
+    dup_sorted = torch.zeros_like(sid, dtype=torch.bool)
+    dup_sorted[:, 1:] = sid[:, 1:] == sid[:, :-1]
+    dup = torch.zeros_like(dup_sorted).scatter(1, by_id, dup_sorted)
+    ids = torch.where(dup, torch.full_like(ids, MAXINT), ids)
+    cls = torch.where(dup | (ids == MAXINT), torch.full_like(cls, 3.0), cls)
+    keep_order = torch.argsort(cls, dim=1, stable=True)[:, :d]
+    ids = torch.gather(ids, 1, keep_order).contiguous()
+    dist = torch.gather(dist, 1, keep_order)
+    dist = torch.where(ids == MAXINT, torch.full_like(dist, MAXFLOAT), dist).contiguous()
+    sort_pairs_(ids, dist, dedup=False)
+    return ids, dist
