@@ -27,7 +27,7 @@ import sys
 import threading
 import types
 
-REFERENCE_ROOT = os.environ.get("VL_REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("VL_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
 
 
 def _parse_constants(path):

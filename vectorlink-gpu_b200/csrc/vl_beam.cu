@@ -31,6 +31,15 @@
 
 namespace {
 
+#ifndef VL_MB
+#define VL_MB 4     // CTAs per SM the register allocation aims for (4 x 4 warps measured fastest)
+#endif
+#ifndef VL_PB
+#define VL_PB 6     // chunks of 32 candidates per round of id / memo loads
+#endif
+#ifndef VL_U8
+#define VL_U8 2     // gather steps in flight for rows of 8 chunks per lane
+#endif
 constexpr int kBeamWarps = 4;             // most warps (= rows in flight) per CTA
 constexpr int32_t kHashEmpty = -1;
 
@@ -204,7 +213,7 @@ __device__ __noinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int len
 
 // JU > 0: exact-fit rows (dim == 4*LPR*JU, see vl_load_exact); JU == 0: any dim % 4 == 0.
 template <int LPR, int JP, int JU, int METRIC>
-__global__ void __launch_bounds__(kBeamWarps * 32, 4)
+__global__ void __launch_bounds__(kBeamWarps * 32, VL_MB)
 beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -336,7 +345,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             // ---- neighbour ids of the popped nodes (kernels.py:244), then which of them need a
             // gather: live ids the memo does not know.  Four chunks of 32 candidates per round so
             // that the graph-row loads, and then the memo loads, of a round are in flight together.
-            constexpr int PB = 6;   // chunks of 32 candidates per round of loads
+            constexpr int PB = VL_PB;
             int n_todo = 0;
             const bool raw_iteration = p.dump_last && k == p.n_iters;   // needs every real distance
 #pragma unroll 1
@@ -386,7 +395,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             st_iter += 1;
             VL_PHASE(1);   // neighbour ids + memo probe
             // ---- gathered distances (kernels.py:248-257): G rows per step, U steps in flight ----
-            constexpr int U = (QSMEM || JQ <= 4) ? 2 : 1;
+            constexpr int U = QSMEM ? VL_U8 : (JQ <= 4 ? 2 : 1);
 #pragma unroll 1
             for (int t0 = 0; t0 < n_todo; t0 += U * G) {
                 bool live[U];
