@@ -154,16 +154,32 @@ __device__ __forceinline__ vl_f2 vl_f2_sub(vl_f2 a, vl_f2 b)
     asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-// Products stay scalar: ptxas 12.9 contracts a packed multiply with the packed add that
-// consumes it into one packed FMA (one rounding instead of two) even when both carry .rn,
-// which would break bit parity; a scalar FMUL feeding a packed add is left alone.
+// Packed product.  ptxas 12.9 contracts a packed multiply (and a packed FMA with a -0 addend,
+// which it may simplify to a multiply) with the packed add that consumes it into one packed
+// FMA - one rounding instead of two, which breaks bit parity - even when both carry .rn.
+// fma(a, b, +0) cannot be simplified (it differs from a*b when the product is -0) and an FMA
+// cannot absorb a following add, so this form keeps both roundings.  Its value is round(a*b)
+// except that a -0 product becomes +0, which no sum downstream can tell apart.
+__device__ __forceinline__ vl_f2 vl_f2_mul(vl_f2 a, vl_f2 b)
+{
+    vl_f2 d;
+    const vl_f2 zero = 0ull;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(zero));
+    return d;
+}
 template <int METRIC>
 __device__ __forceinline__ vl_f2 vl_f2_term(float ax, float ay, float bx, float by)
 {
+#ifndef VL_PACKED_PRODUCTS   // default: scalar products (measured equally fast, and independent of how ptxas treats packed FMAs)
     if (METRIC == VL_METRIC_COSINE) return vl_f2_pack(__fmul_rn(ax, bx), __fmul_rn(ay, by));
     float dx, dy;
     vl_f2_unpack(vl_f2_sub(vl_f2_pack(ax, ay), vl_f2_pack(bx, by)), dx, dy);
     return vl_f2_pack(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+#else
+    if (METRIC == VL_METRIC_COSINE) return vl_f2_mul(vl_f2_pack(ax, ay), vl_f2_pack(bx, by));
+    const vl_f2 d = vl_f2_sub(vl_f2_pack(ax, ay), vl_f2_pack(bx, by));
+    return vl_f2_mul(d, d);
+#endif
 }
 
 // Exact-fit distance on packed pairs: (x,y) and (z,w) of every chunk travel as fp32x2 through
