@@ -275,3 +275,28 @@ def test_full_size_properties_config2_slice(built_lib):
     srt = b.sort(dim=1).values
     assert bool(((srt[:, 1:] != srt[:, :-1]) | (srt[:, 1:] == MAXINT)).all())
     assert torch.equal(calculate_distances(vectors, b, metric="l2"), d)
+
+
+def test_layered_search_and_recall_helpers(c1, built_lib):
+    """search_layers / hnsw_calculate_recall (ann.py:96-106, 262-284) over a one-layer list equal
+    the flat self-recall; ann_calculate_recall on the fixture graph finds every sampled row."""
+    from vectorlink_gpu.ann import ann_calculate_recall, hnsw_calculate_recall
+    cfg, _ = cfg_of(c1)
+    v, b = t(c1["vectors"]), t(c1["beams"])
+    flat = ann_calculate_recall(v, b, cfg, sample=v[:500])
+    layered = hnsw_calculate_recall(v, [b], cfg, sample=v[:500])
+    assert flat == layered and flat[0] == oracle.self_recall(c1["vectors"], c1["beams"], cfg, 500)
+
+
+@pytest.mark.parametrize("batch_size", [1, 3, 50])
+def test_build_with_tiny_batches_follows_the_reference_batch_coupling(batch_size, built_lib):
+    """With batches of a few rows the reference's per-batch early exit happens inside the build;
+    the single-launch build must repair exactly those batches."""
+    from vectorlink_gpu.ann import generate_ann
+    rng = np.random.default_rng(123)
+    vectors = unit(rng, 240, 24)
+    cfg = oracle.make_config(beam_size=6, batch_size=batch_size, optimization_loops=2)
+    wb, wd, loops, found = oracle.generate_ann(vectors, cfg)
+    gb, gd = generate_ann(t(vectors), dict(cfg))
+    assert generate_ann.last_loops == loops
+    assert np.array_equal(n(gb), wb) and np.array_equal(n(gd), wd)

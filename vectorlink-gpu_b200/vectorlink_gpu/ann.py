@@ -447,6 +447,21 @@ def ann_calculate_recall(vectors: Tensor, beams: Tensor, config: Dict, sample: O
     return (found, found / sample_size)
 
 
+def hnsw_calculate_recall(vectors: Tensor, hnsw: List[Tensor], config: Dict, sample: Optional[Tensor] = None):
+    """ann.py:262-284: self-recall through a list of layer graphs, coarsest first."""
+    if sample is None:
+        sample = vectors
+    (sample_size, _) = sample.size()
+    queue = initial_queue(sample.contiguous(), config)
+    search_layers([layer.contiguous() for layer in hnsw], sample.contiguous(), queue, vectors, config)
+    expected = torch.arange(sample_size, device=vectors.device)
+    actual = queue.indices.t()[0]
+    found = (expected == actual).sum().item()
+    print_timestamp(f"found: {found} / {sample_size}")
+    print_timestamp(f"recall: {found / sample_size}")
+    return (found, found / sample_size)
+
+
 def ann_recall_test(vectors: Tensor, config: Dict):
     """ann.py:287-293."""
     (beams, _) = generate_ann(vectors, config)
