@@ -119,6 +119,54 @@ __device__ __forceinline__ float vl_tree_reduce(float4 (&acc)[JP])
     return __fadd_rn(__fadd_rn(a.x, a.z), __fadd_rn(a.y, a.w));
 }
 
+// L2 eviction-priority hints (createpolicy + ld/st ...L2::cache_hint): candidate rows are streamed
+// (evict first), while a row's memo and the graph rows are what the next iterations come back to
+// (evict last).
+__device__ __forceinline__ uint64_t vl_policy_evict_first()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t vl_policy_evict_normal()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t vl_policy_evict_last()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ float4 vl_ldg_hint(const float4* ptr, uint64_t pol)
+{
+    float4 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ int32_t vl_ldg_hint(const int32_t* ptr, uint64_t pol)
+{
+    int32_t v;
+    asm volatile("ld.global.nc.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(ptr), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ ulonglong2 vl_ld_hint(const ulonglong2* ptr, uint64_t pol)
+{
+    ulonglong2 v;
+    asm volatile("ld.global.L2::cache_hint.v2.u64 {%0,%1}, [%2], %3;" : "=l"(v.x), "=l"(v.y) : "l"(ptr), "l"(pol) : "memory");
+    return v;
+}
+template <int LPR, int JU>
+__device__ __forceinline__ void vl_load_exact_hint(const float* __restrict__ row, int lg, float4 (&xr)[JU], uint64_t pol)
+{
+    const float4* r4 = reinterpret_cast<const float4*>(row) + lg;
+#pragma unroll
+    for (int j = 0; j < JU; ++j) xr[j] = vl_ldg_hint(r4 + LPR * j, pol);
+}
+
 // Exact-fit fast path: the row is exactly LPR*JU 16-byte chunks (dim == 4*LPR*JU <= 1024,
 // aligned), so every lane loads JU chunks with no bounds test; `row` must be a readable row
 // even for a dead candidate (its result is discarded).
