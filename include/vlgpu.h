@@ -102,7 +102,8 @@ int vl_seen_add_noalloc(int32_t* seen, int64_t b, int e, const int32_t* visit, i
 
 /* prune_ (kernels.py:441-468, kernel 409-438) followed by the cut to the first out_cols
  * columns (ann.py:190-193): rows of beams/dist [n, w], sorted by distance on entry, lose the
- * links x->z that have a detour over y's first neighbour (do_punch != 0), are ordered by
+ * links x->z that have a detour over y's first neighbour (do_punch == 1; do_punch == 2 scans every
+ * neighbour of y, the scan the reference's comment describes but its launch shape never ran), are ordered by
  * (distance, id) with sentinels last, and their first out_cols columns are written to the
  * outputs [n, out_cols].  Inputs are not modified.  w <= 2048. */
 int vl_prune(const int32_t* beams, const float* dist, int64_t n, int w, int do_punch, int32_t* beams_out,

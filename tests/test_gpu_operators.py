@@ -231,3 +231,39 @@ def test_symmetrize_adds_reverse_edges_and_keeps_rows_well_formed(built_lib):
     fwd = [set(row) for row in kn]
     gained = sum(1 for x in range(800) for y in ids[x] if y != MAXINT and y not in fwd[x] and x in fwd[y])
     assert gained > 0
+
+
+def test_full_prune_scan_vs_numpy(built_lib):
+    """prune_(full=True): every neighbour of y is a detour witness; rows in rising slot order see
+    their own punches, other rows are read as they came in."""
+    from vectorlink_gpu.kernels import prune_
+    rng = np.random.default_rng(21)
+    rows, w = 120, 10
+    v = unit(rng, rows, 6)
+    full = ((1.0 - v @ v.T) / 2.0).astype(np.float32)
+    np.fill_diagonal(full, np.inf)
+    order = np.argsort(full, axis=1, kind="stable")[:, :w].astype(np.int32)
+    d = np.take_along_axis(full, order, axis=1).astype(np.float32)
+    wb, wd = order.copy(), d.copy()
+    for x in range(rows):
+        for s in range(w):
+            y = wb[x, s]
+            if y == MAXINT:
+                continue
+            hits = []
+            for j in range(w):                         # one warp pass: all lanes decide, then punch
+                z, dz = order[y, j], d[y, j]
+                xi = -1
+                for i in range(w):
+                    if wb[x, i] == z:
+                        xi = i
+                if xi >= 0 and wd[x, xi] > wd[x, s] and wd[x, xi] > dz:
+                    hits.append(xi)
+            for xi in hits:
+                wb[x, xi], wd[x, xi] = MAXINT, np.float32(oracle.MAXFLOAT)
+    key = np.lexsort((wb, wd), axis=1)
+    wb, wd = np.take_along_axis(wb, key, 1), np.take_along_axis(wd, key, 1)
+    gb, gd = prune_(t(order), t(d), full=True)
+    assert np.array_equal(n(gb), wb) and np.array_equal(n(gd), wd)
+    fb, _ = prune_(t(order), t(d))
+    assert (n(gb) == MAXINT).sum() > (n(fb) == MAXINT).sum()       # prunes more than the first-neighbour test

@@ -55,7 +55,7 @@ prune_kernel(const int32_t* __restrict__ beams, const float* __restrict__ dist, 
             d[s] = dxy;
             int32_t z = VL_MAXINT;
             float dz = VL_MAXFLOAT;
-            if (do_punch && y != VL_MAXINT) {
+            if (do_punch == 1 && y != VL_MAXINT) {
                 if (y < 0 || (int64_t)y >= n) atomicOr(status, VL_STATUS_BAD_ID);
                 else { z = beams[(int64_t)y * w]; dz = dist[(int64_t)y * w]; }
             }
@@ -63,7 +63,30 @@ prune_kernel(const int32_t* __restrict__ beams, const float* __restrict__ dist, 
             dyz[s] = dz;
         }
         __syncwarp();
-        if (do_punch) {
+        if (do_punch == 2) {
+            // The scan the authors describe (kernels.py:441-457) but never ran: every neighbour z
+            // of y is a possible detour witness, not only y's first one.  Rows of y come from the
+            // input buffers; row x sees its own earlier punches, slots in rising order.
+            for (int s = 0; s < w; ++s) {
+                const int32_t y = ids[s];
+                if (y == VL_MAXINT || y < 0 || (int64_t)y >= n) continue;
+                const float dxy = d[s];
+                for (int j0 = 0; j0 < w; j0 += 32) {
+                    const int j = j0 + lane;
+                    int32_t z = VL_MAXINT;
+                    float dz = VL_MAXFLOAT;
+                    if (j < w) { z = beams[(int64_t)y * w + j]; dz = dist[(int64_t)y * w + j]; }
+                    // each lane looks its z up in row x (last matching slot), then punches
+                    int xi = -1;
+                    if (z != VL_MAXINT)
+                        for (int i = 0; i < w; ++i) if (ids[i] == z) xi = i;
+                    const bool hit = xi >= 0 && d[xi] > dxy && d[xi] > dz;
+                    __syncwarp();
+                    if (hit) { ids[xi] = VL_MAXINT; d[xi] = VL_MAXFLOAT; }
+                    __syncwarp();
+                }
+            }
+        } else if (do_punch) {
             for (int s = 0; s < w; ++s) {
                 if (ids[s] == VL_MAXINT) continue;       // warp-uniform: shared reads
                 int32_t z = zs[s];

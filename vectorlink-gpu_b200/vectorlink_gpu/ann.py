@@ -368,7 +368,7 @@ def generate_ann(vectors: Tensor, config: Dict, group=None) -> Tuple[Tensor, Ten
             _share_rows(next_beam_distances, bounds, group)
 
         if config["prune"]:
-            (beams, beam_distances) = prune_(next_beams, next_beam_distances)
+            (beams, beam_distances) = prune_(next_beams, next_beam_distances, full=config.get("prune_mode") == "full")
         else:
             (beams, beam_distances) = (next_beams, next_beam_distances)
         loops_run += 1
@@ -483,14 +483,16 @@ class ANN:
     `.distances` fp32 [N, beam_size], `.search(query)` returns the search `Queue`.
     Added keywords: metric ("cosine" - the reference's distance on unit vectors - or "l2") and
     search_seed_factor (how many times Q seeds `.search` scans for its starting queue; 1 = the
-    reference), symmetrize (add reverse edges after the build; off = the reference) and group (a torch.distributed group whose ranks all pass the same vectors: the
+    reference), prune_mode ("first" = the reference's detour test against y's first neighbour only,
+    "full" = against all of them), symmetrize (add reverse edges after the build; off = the reference) and group (a torch.distributed group whose ranks all pass the same vectors: the
     build's rows are split across them, see generate_ann)."""
 
     def __init__(self, vectors: Tensor, prune: bool = True, beam_size: int = 24, parallel_visit_count: int = 4,
                  beam_queue_factor: int = 3, visit_queue_factor: int = 3, exclude_factor: int = 5,
                  optimization_loops: int = 3, batch_size: int = 10_000, recall_search_queue_factor: int = 3,
                  speculative_readahead: int = 5, beams: Optional[Tensor] = None, distances: Optional[Tensor] = None,
-                 metric: str = "cosine", search_seed_factor: int = 1, group=None, symmetrize: bool = False):
+                 metric: str = "cosine", search_seed_factor: int = 1, group=None, symmetrize: bool = False,
+                 prune_mode: str = "first"):
         (count, dim) = vectors.size()
         assert vectors.dtype == torch.float32
         _lib.require_cuda(vectors)
@@ -511,6 +513,9 @@ class ANN:
             self.configuration["metric"] = metric
         if search_seed_factor != 1:
             self.configuration["search_seed_factor"] = search_seed_factor
+        assert prune_mode in ("first", "full")
+        if prune_mode != "first":
+            self.configuration["prune_mode"] = prune_mode
         self.vectors = vectors.contiguous()
         wall_start = time.time()
         if beams is not None:

@@ -120,10 +120,12 @@ def punchout_duplicates_(ids: Tensor, distances: Tensor):
     return (ids, distances)
 
 
-def prune_(beams: Tensor, distances: Tensor, out_cols: Optional[int] = None, punch: bool = True):
+def prune_(beams: Tensor, distances: Tensor, out_cols: Optional[int] = None, punch: bool = True, full: bool = False):
     """kernels.py:441-468: remove detourable links (x->z when d_xz > d_xy and d_xz > d_yz, z the
     first neighbour of y), then order every row by distance.  Returns new (beams, distances);
-    `out_cols` (added) keeps only the first columns."""
+    `out_cols` (added) keeps only the first columns; `full` (added) tests every neighbour of y as the
+    detour witness, which is what the reference's docstring describes (its launch only ever
+    looks at y's first neighbour)."""
     assert beams.dtype == torch.int32
     assert distances.dtype == torch.float32
     assert beams.is_contiguous() and distances.is_contiguous()
@@ -132,7 +134,7 @@ def prune_(beams: Tensor, distances: Tensor, out_cols: Optional[int] = None, pun
     cols = beam_size if out_cols is None else out_cols
     out_b = torch.empty((batch_size, cols), dtype=torch.int32, device=beams.device)
     out_d = torch.empty((batch_size, cols), dtype=torch.float32, device=beams.device)
-    check(lib().vl_prune(ptr(beams), ptr(distances), ctypes.c_int64(batch_size), beam_size, 1 if punch else 0,
+    check(lib().vl_prune(ptr(beams), ptr(distances), ctypes.c_int64(batch_size), beam_size, (2 if full else 1) if punch else 0,
                          ptr(out_b), ptr(out_d), cols, ptr(_lib.status_word(beams.device)), stream_of(beams)),
           "vl_prune")
     return (out_b, out_d)
