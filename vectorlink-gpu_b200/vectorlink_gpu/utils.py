@@ -36,8 +36,10 @@ def generate_queue_circulants(batch_size: int, num_vecs: int, primes: Tensor, fi
     """utils.py:26-32: seeds[b, j] = sort_j(b + p_j) mod num_vecs; `first_row` (added) numbers the
     rows from there, for a batch that is a slice of a larger one."""
     indices = torch.arange(first_row, first_row + batch_size, device=primes.device, dtype=torch.int32)
-    circulant_neighbors = indices.unsqueeze(1) + primes.unsqueeze(0)
-    return (circulant_neighbors.sort().values % num_vecs).contiguous()
+    # the reference sorts every row of (b + p_j); adding b keeps the order, so sorting the offsets once
+    # gives the same rows
+    circulant_neighbors = indices.unsqueeze(1) + primes.sort().values.unsqueeze(0)
+    return (circulant_neighbors % num_vecs).contiguous()
 
 
 def generate_circulant_beams(num_vecs: int, primes: Tensor) -> Tensor:
