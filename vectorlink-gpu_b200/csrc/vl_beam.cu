@@ -348,7 +348,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             }
             VL_PHASE(0);   // pop
             // ---- neighbour ids of the popped nodes (kernels.py:244), then which of them need a
-            // gather: live ids the memo does not know.  Four chunks of 32 candidates per round so
+            // gather: live ids the memo does not know.  VL_PB chunks of 32 candidates per round so
             // that the graph-row loads, and then the memo loads, of a round are in flight together.
             constexpr int PB = VL_PB;
             int n_todo = 0;
@@ -457,13 +457,14 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     vl_key_t key = candk[i];
                     int32_t id = vl_key_id(key);
                     bool drop = (id == self_id);
-                    if (!drop && excl)
+                    if (!drop && excl) {
 #pragma unroll 1
                         for (int t = 0; t < p.exclude_w; ++t) {
                             int32_t x = excl[t];
                             if (x == VL_MAXINT) break;
                             if (x == id) { drop = true; break; }
                         }
+                    }
                     if (drop) key = kSent;
                     p.out_ids[row * p.out_ld + sq_len + i] = vl_key_id(key);
                     p.out_dist[row * p.out_ld + sq_len + i] = vl_key_dist(key);
@@ -491,13 +492,14 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 if (want) {
                     int32_t id = vl_key_id(key);
                     if (id == self_id) want = false;
-                    else if (excl)
+                    else if (excl) {
 #pragma unroll 1
                         for (int x = 0; x < p.exclude_w; ++x) {   // kernels.py:478-488
                             int32_t ex = excl[x];
                             if (ex == VL_MAXINT) break;
                             if (ex == id) { want = false; break; }
                         }
+                    }
                 }
                 if (!__any_sync(0xffffffffu, want)) continue;
                 changed |= merge_chunk(sq, sq_n, sq_len, key, want, lane, mpos);
