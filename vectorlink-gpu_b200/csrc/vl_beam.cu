@@ -415,6 +415,24 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     rp[u] = p.vectors + (int64_t)id * p.dim;
                 }
                 float dd[U];
+#ifndef VL_NO_PREFETCH
+                if constexpr (JU > 0) {
+                    // pull the next round of candidate rows into L1 while this one is reduced: the
+                    // registers can only hold one round of rows, the cache can hold the next
+                    constexpr int LINES = (4 * LPR * JU * 4) / 128;          // 128-byte lines per row
+                    const int tn = t0 + U * G;
+#pragma unroll
+                    for (int l0 = 0; l0 < U * G * LINES; l0 += 32) {
+                        const int l = l0 + lane;
+                        const int t = tn + l / LINES;
+                        if (l < U * G * LINES && t < n_todo) {
+                            const int32_t nid = (int32_t)cand[todo[t]].x;
+                            const float* np_ = p.vectors + (int64_t)nid * p.dim + (l % LINES) * 32;
+                            asm volatile("prefetch.global.L1 [%0];" : : "l"(np_));
+                        }
+                    }
+                }
+#endif
                 if constexpr (JU > 0) {
                     float4 x[U][JU];
 #pragma unroll
