@@ -601,8 +601,35 @@ class ANN:
         row depend on its index)."""
         assert query.dtype == torch.float32
         query = query.contiguous()
-        search_queue = initial_search_queue(self.vectors, query, self.configuration, first_row)
-        closest_vectors(query, search_queue, self.vectors, self.beams, self.configuration, None)
+        config = self.configuration
+        queue_size = config["recall_search_queue_factor"] * config["beam_size"]
+        extra_capacity = max(queue_size, config["parallel_visit_count"] * config["beam_size"])
+        seed_count = queue_size * max(1, int(config.get("search_seed_factor", 1)))
+        beams = self.beams.contiguous()
+        if (seed_count > extra_capacity and query.size(0) > 0 and not config.get("stepwise", False)
+                and _fused_shape_ok(self.vectors, beams.size(1), queue_size, queue_size + extra_capacity, config)):
+            # widened seed scan: the fused kernel starts every row from an empty queue and merges the
+            # seeds itself, so the best-Q selection needs no separate sort
+            _lib.require_cuda(query, self.vectors, beams)
+            dev = self.vectors.device
+            seeds = generate_queue_circulants(query.size(0), self.vectors.size(0), primes(seed_count, dev), first_row)
+            d = query_distances(query, self.vectors, seeds, _metric_of(config))
+            queue = Queue(query.size(0), queue_size, queue_size + extra_capacity, device=dev)
+
+            def stepwise(lo, hi):
+                q = initial_search_queue(self.vectors, query, config, first_row)
+                n = closest_vectors_stepwise(query, q, self.vectors, beams, config, None)
+                queue.indices.copy_(q.indices)
+                queue.distances.copy_(q.distances)
+                return n
+
+            counts = _fused_batches(self.vectors, beams, query, seeds, d, seed_count, queue_size,
+                                    queue_size + extra_capacity, config, None, -1, query.size(0), queue.indices,
+                                    queue.distances, queue_size + extra_capacity, stepwise)
+            closest_vectors.last_count = counts[0]
+            return queue
+        search_queue = initial_search_queue(self.vectors, query, config, first_row)
+        closest_vectors(query, search_queue, self.vectors, beams, config, None)
         return search_queue
 
     def dump_logs(self) -> Dict:
