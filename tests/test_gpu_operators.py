@@ -100,7 +100,8 @@ def test_queue_operator_trace_vs_reference_host_code(c1, built_lib):
     assert np.array_equal(n(changed), c1["op_q2_changed"])
 
 
-@pytest.mark.parametrize("cap,length,m", [(28, 12, 16), (480, 96, 384), (960, 192, 768), (33, 1, 32), (2, 1, 1)])
+@pytest.mark.parametrize("cap,length,m", [(28, 12, 16), (480, 96, 384), (960, 192, 768), (33, 1, 32), (2, 1, 1),
+                                          (4096, 1000, 3096), (64, 32, 0)])
 def test_queue_insert_random_vs_oracle(built_lib, cap, length, m):
     from vectorlink_gpu.queue import Queue
     rng = np.random.default_rng(cap)

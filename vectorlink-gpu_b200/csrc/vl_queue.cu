@@ -248,7 +248,7 @@ extern "C" int vl_queue_insert(int32_t* ids, float* dist, int64_t b, int cap, in
                                const int32_t* cand_ids, const float* cand_dist, int m,
                                const int32_t* excl, int e, uint8_t* changed, void* stream)
 {
-    VL_CHECK_ARG(ids && dist && cand_ids && cand_dist, "vl_queue_insert: null pointer");
+    VL_CHECK_ARG(ids && dist && (m == 0 || (cand_ids && cand_dist)), "vl_queue_insert: null pointer");
     VL_CHECK_ARG(cap > 0 && cap <= kMaxSortWidth, "vl_queue_insert: capacity %d outside 1..%d", cap, kMaxSortWidth);
     VL_CHECK_ARG(length >= 0 && m >= 0 && m <= cap - length, "vl_queue_insert: %d candidates do not fit behind %d of %d columns", m, length, cap);
     VL_CHECK_ARG(excl || e == 0, "vl_queue_insert: exclusion width without a list");
