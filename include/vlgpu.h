@@ -117,6 +117,14 @@ int vl_prune(const int32_t* beams, const float* dist, int64_t n, int w, int do_p
 int vl_reverse_edges(const int32_t* beams, int64_t n, int d, int scan, int phase, int32_t* deg, const int64_t* offsets,
                      int32_t* cursor, unsigned long long* keys, int keep, int32_t* out, int* status, void* stream);
 
+/* Cluster extraction, announced by the reference on top of "all search queues" (README.md:24) but
+ * left as an empty stub (ANN.clusters, ann.py:466-467): connected components of the neighbour
+ * lists ids/dist [n, w] (row stride ld elements).  x and y = ids[x, s] are linked, in both
+ * directions, when y != MAXINT and dist[x, s] <= threshold (every real id when dist == NULL).
+ * labels[x] (int32 [n]) = the smallest node id of x's component. */
+int vl_connected_components(const int32_t* ids, const float* dist, int64_t n, int w, int64_t ld, float threshold,
+                            int32_t* labels, int* status, void* stream);
+
 /* closest_vectors (ann.py:37-93) as one kernel: the whole budgeted beam search of every query
  * row, with the search queue, the visit queue and the visited set of a row held on chip by
  * one warp.  Replaces, per iteration, pop_n_ids + search_from_seeds + two Queue.insert +

@@ -70,6 +70,7 @@ def lib():
         _lib = ctypes.CDLL(_SO)
         _lib.vlo_pair_distance.restype = ctypes.c_float
         _lib.vlo_self_recall.restype = ctypes.c_int64
+        _lib.vlo_connected_components.restype = ctypes.c_int64
         for name in ("vlo_queue_pop", "vlo_add_new_to_seen", "vlo_closest_vectors", "vlo_generate_ann",
                      "vlo_num_threads"):
             getattr(_lib, name).restype = ctypes.c_int
@@ -344,3 +345,16 @@ def bruteforce_knn(vectors, queries, k: int, metric=COSINE, exclude_self: bool =
                              ctypes.c_int(metric_code(metric)), ctypes.c_int(1 if exclude_self else 0),
                              _L(self_base), _p(out, _I))
     return out
+
+
+def connected_components(ids, dist=None, threshold: float = MAXFLOAT):
+    """(labels int32 [N], count of out-of-range ids): labels[x] = the smallest id of the connected
+    component of x in the graph linking x and ids[x, s] wherever the id is real and
+    dist[x, s] <= threshold.  Not in the reference (its `ANN.clusters` is a stub)."""
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    n, w = ids.shape
+    d = _f32(dist) if dist is not None else None
+    labels = np.empty(n, dtype=np.int32)
+    bad = lib().vlo_connected_components(_p(ids, _I), _p(d, _F) if d is not None else None, _L(n), ctypes.c_int(w),
+                                         ctypes.c_float(threshold), _p(labels, _I))
+    return labels, int(bad)

@@ -553,6 +553,37 @@ void vlo_bruteforce_knn(const float *vectors, int64_t n, int dim, const float *q
     }
 }
 
+static int32_t vlo_uf_find(int32_t *parent, int32_t v)
+{
+    int32_t r = v;
+    while (parent[r] != r) r = parent[r];
+    while (parent[v] != r) { int32_t nx = parent[v]; parent[v] = r; v = nx; }
+    return r;
+}
+
+/* Connected components of a thresholded neighbour graph (not in the reference, whose
+ * ANN.clusters is a stub, ann.py:466-467): sequential union-find, always hooking the larger
+ * root under the smaller, so labels[x] = smallest id of x's component.  dist may be NULL.
+ * Returns the number of ids outside [0, n) that are not MAXINT (they are skipped). */
+int64_t vlo_connected_components(const int32_t *ids, const float *dist, int64_t n, int w, float threshold,
+                                 int32_t *labels)
+{
+    int64_t bad = 0;
+    for (int64_t i = 0; i < n; ++i) labels[i] = (int32_t)i;
+    for (int64_t x = 0; x < n; ++x)
+        for (int s = 0; s < w; ++s) {
+            int32_t y = ids[x * w + s];
+            if (y == VLO_MAXINT) continue;
+            if (y < 0 || y >= n) { ++bad; continue; }
+            if (dist && !(dist[x * w + s] <= threshold)) continue;
+            int32_t a = vlo_uf_find(labels, (int32_t)x), b = vlo_uf_find(labels, y);
+            if (a < b) labels[b] = a;
+            else if (b < a) labels[a] = b;
+        }
+    for (int64_t i = 0; i < n; ++i) labels[i] = vlo_uf_find(labels, (int32_t)i);
+    return bad;
+}
+
 int vlo_num_threads(void)
 {
 #ifdef _OPENMP

@@ -22,7 +22,8 @@ c_intp = ctypes.POINTER(ctypes.c_int)
 EXPORTS = [
     "vl_last_error", "vl_abi_version", "vl_calculate_distances", "vl_search_from_seeds", "vl_queue_insert",
     "vl_queue_pop", "vl_punchout_excluded", "vl_dedup_adjacent", "vl_sort_pairs", "vl_dedup_sort_ids",
-    "vl_seen_add", "vl_seen_add_noalloc", "vl_prune", "vl_reverse_edges", "vl_beam_search", "vl_beam_search_plan",
+    "vl_seen_add", "vl_seen_add_noalloc", "vl_prune", "vl_reverse_edges", "vl_connected_components", "vl_beam_search",
+    "vl_beam_search_plan",
 ]
 
 
@@ -78,12 +79,13 @@ def lib() -> ctypes.CDLL:
         _lib.vl_seen_add_noalloc.argtypes = [P, L, I, P, I, P, P]
         _lib.vl_prune.argtypes = [P, P, L, I, I, P, P, I, P, P]
         _lib.vl_reverse_edges.argtypes = [P, L, I, I, I, P, P, P, P, I, P, P, P]
+        _lib.vl_connected_components.argtypes = [P, P, L, I, L, ctypes.c_float, P, P, P]
         _lib.vl_beam_search.argtypes = [ctypes.POINTER(BeamParams), P]
         _lib.vl_beam_search_plan.argtypes = [ctypes.POINTER(BeamParams), c_intp, c_intp, c_intp]
     return _lib
 
 
-KERNELS_PER_CALL = {"vl_dedup_adjacent": 2, "vl_seen_add": 3, "vl_seen_add_noalloc": 3}   # every other entry point launches one
+KERNELS_PER_CALL = {"vl_dedup_adjacent": 2, "vl_seen_add": 3, "vl_seen_add_noalloc": 3, "vl_connected_components": 3}   # every other entry point launches one
 
 
 def check(rc: int, what: str) -> None:

@@ -19,7 +19,7 @@ from torch import Tensor
 from . import _lib
 from ._lib import BeamParams, check, lib, ptr, stream_of
 from .constants import MAXFLOAT, MAXINT, PRIMES_HOST
-from .kernels import calculate_distances, metric_code, prune_, search_from_seeds, sort_pairs_
+from .kernels import calculate_distances, connected_components, metric_code, prune_, search_from_seeds, sort_pairs_
 from .log import log_time
 from . import log as _log
 from .queue import Queue
@@ -592,6 +592,15 @@ class ANN:
         queue = initial_queue(self.vectors, self.configuration)
         closest_vectors(self.vectors, queue, self.vectors, self.beams, self.configuration)
         return queue
+
+    def cluster_labels(self, threshold: float, queues: Optional[Queue] = None) -> Tensor:
+        """Clusters as connected components (added; the reference stops at the `clusters` stub):
+        int32 [N] labels, the smallest vector id of each component of the graph whose links are
+        the neighbour pairs at distance <= threshold.  Links come from the graph's own rows
+        (`.beams` / `.distances`), or from the heads of `queues` as returned by `clusters()`."""
+        if queues is None:
+            return connected_components(self.beams, self.distances, threshold)
+        return connected_components(queues.indices[:, :queues.length], queues.distances[:, :queues.length], threshold)
 
     def search(self, query: Tensor, first_row: int = 0) -> Queue:
         """ann.py:469-477: `query` fp32 [B, dim] -> Queue with `.indices` int32 and `.distances`

@@ -194,6 +194,31 @@ def reverse_edges(beams: Tensor, scan: Optional[int] = None, keep: Optional[int]
     return out
 
 
+def connected_components(ids: Tensor, distances: Optional[Tensor] = None, threshold: float = MAXFLOAT) -> Tensor:
+    """Cluster labels of a neighbour graph: int32 [N], the smallest id of each node's connected
+    component, where x and ids[x, s] are linked (both ways) when the id is real and
+    distances[x, s] <= threshold.  `ids` int32 [N, w] may be a column slice of a wider tensor
+    (a Queue head).  The step the reference announces for `ANN.clusters` (README.md:24) and
+    leaves as a stub (ann.py:466-467)."""
+    assert ids.dtype == torch.int32 and ids.dim() == 2
+    assert distances is None or (distances.dtype == torch.float32 and distances.size() == ids.size())
+    _lib.require_cuda(ids, distances)
+    (n, w) = ids.size()
+    sliced = n > 1 and w > 0 and ids.stride(1) == 1 and ids.stride(0) >= w
+    if sliced and (distances is None or distances.stride() == ids.stride()):
+        ld = ids.stride(0)
+    else:
+        ids = ids.contiguous()
+        distances = distances.contiguous() if distances is not None else None
+        ld = w
+    labels = torch.empty(n, dtype=torch.int32, device=ids.device)
+    status = _lib.status_word(ids.device)
+    check(lib().vl_connected_components(ptr(ids), ptr(distances), n, w, ld,
+                                        float(threshold), ptr(labels), ptr(status), stream_of(ids)),
+          "vl_connected_components")
+    return labels
+
+
 def symmetrize(vectors: Tensor, beams: Tensor, distances: Tensor, keep: Optional[int] = None, metric="cosine"):
     """The intent of the reference's `symmetrize` sketch (utils.py:92-103, dead code): give every
     node up to `keep` (default half its degree) of its reverse edges.  The new row is the
