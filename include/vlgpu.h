@@ -171,6 +171,8 @@ typedef struct vl_beam_params {
                                   neighbour ids, memo probe, gather, memo update, search-queue merge, visit-queue merge */
     int32_t flags;             /* bit 0: also accumulate the per-phase cycle counters of `stats` */
     int32_t reserved;
+    unsigned long long* row_ticket; /* optional device counter, zero at launch: warps then draw their next row from it
+                                  (rows that take unequal time no longer wait for a fixed partner); NULL = fixed stride */
 } vl_beam_params;
 
 int vl_beam_search(const vl_beam_params* params, void* stream);

@@ -87,12 +87,15 @@ def test_ann_constructor_is_a_drop_in(c1, built_lib):
     assert (n(clusters.indices[:, 0]) == np.arange(2000)).mean() > 0.99
 
 
-def closest_both(vectors, beams, queries, oq, cfg, exclude=None, metric="cosine", stepwise=False, memo=True):
+def closest_both(vectors, beams, queries, oq, cfg, exclude=None, metric="cosine", stepwise=False, memo=True,
+                 row_ticket=True):
     from vectorlink_gpu.ann import closest_vectors
     gq = gpu_queue_from(oq)
     config = dict(cfg)
     if not memo:
         config["memo"] = False
+    if not row_ticket:
+        config["row_ticket"] = False
     if metric != "cosine":
         config["metric"] = metric
     if stepwise:
@@ -155,6 +158,24 @@ def test_distance_memo_changes_nothing(built_lib):
     for memo in (True, False):
         oq = oracle.initial_search_queue(vectors, queries, cfg)
         gq, oq, gcount, ocount = closest_both(vectors, kn, queries, oq, cfg, memo=memo)
+        assert gcount == ocount
+        assert np.array_equal(n(gq.indices), oq.indices) and np.array_equal(n(gq.distances), oq.distances)
+        results.append(n(gq.indices))
+    assert np.array_equal(results[0], results[1])
+
+
+def test_row_schedule_changes_nothing(built_lib):
+    """More rows than the launch keeps in flight: warps that draw their next row from the shared
+    counter and warps on a fixed stride produce the same queues, equal to the oracle's."""
+    rng = np.random.default_rng(77)
+    vectors = unit(rng, 3000, 32)
+    cfg = oracle.make_config(beam_size=8, visit_queue_factor=2, recall_search_queue_factor=2, batch_size=20_000)
+    kn = oracle.bruteforce_knn(vectors, vectors, 8, exclude_self=True)
+    queries = unit(rng, 9000, 32)
+    results = []
+    for ticket in (True, False):
+        oq = oracle.initial_search_queue(vectors, queries, cfg)
+        gq, oq, gcount, ocount = closest_both(vectors, kn, queries, oq, cfg, row_ticket=ticket)
         assert gcount == ocount
         assert np.array_equal(n(gq.indices), oq.indices) and np.array_equal(n(gq.distances), oq.distances)
         results.append(n(gq.indices))

@@ -18,4 +18,4 @@ void vl_set_error(const char* fmt, ...)
 
 extern "C" const char* vl_last_error(void) { return g_error; }
 
-extern "C" int vl_abi_version(void) { return 1; }
+extern "C" int vl_abi_version(void) { return 2; }

@@ -253,8 +253,11 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
     const int wpb = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * wpb + warp;
     const int64_t nwarps = (int64_t)gridDim.x * wpb;
+    // Row schedule: the first row of a warp is fixed; after that either a fixed stride or, when the
+    // caller provides a zeroed counter, the next row nobody has taken yet (rows take unequal time).
+    int64_t row = warp0;
 #pragma unroll 1
-    for (int64_t row = warp0; row < p.rows; row += nwarps) {
+    while (row < p.rows) {
         vl_key_t* sq = reinterpret_cast<vl_key_t*>(base + lay.sq_a);
         vl_key_t* sq_n = reinterpret_cast<vl_key_t*>(base + lay.sq_b);
         vl_key_t* vq = reinterpret_cast<vl_key_t*>(base + lay.vq_a);
@@ -643,6 +646,13 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 for (int i = 0; i < 10; ++i) atomicAdd(p.stats + 8 + i, (unsigned long long)tk[i]);
         }
         __syncwarp();
+        if (p.row_ticket) {
+            unsigned long long t = 0;
+            if (lane == 0) t = atomicAdd(p.row_ticket, 1ull);
+            row = nwarps + (int64_t)__shfl_sync(0xffffffffu, t, 0);
+        } else {
+            row += nwarps;
+        }
     }
 }
 

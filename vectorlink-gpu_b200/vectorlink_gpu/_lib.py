@@ -43,7 +43,7 @@ class BeamParams(ctypes.Structure):
         ("changed_flags", ctypes.c_void_p), ("n_checks", ctypes.c_int32), ("memo_entries", ctypes.c_int32),
         ("group_full", ctypes.c_void_p), ("status", ctypes.c_void_p),
         ("memo", ctypes.c_void_p), ("memo_slots", ctypes.c_int64), ("stats", ctypes.c_void_p),
-        ("flags", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("flags", ctypes.c_int32), ("reserved", ctypes.c_int32), ("row_ticket", ctypes.c_void_p),
     ]
 
 

@@ -108,6 +108,9 @@ def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len
     p.memo_slots = 0
     p.stats = STATS.data_ptr() if STATS is not None else 0
     p.flags = 1 if (STATS is not None and STATS_TIMERS) else 0
+    # rows differ in the work they take: warps draw their next row from a counter instead of a fixed stride
+    ticket = torch.zeros(1, dtype=torch.int64, device=vectors.device) if config.get("row_ticket", True) else None
+    p.row_ticket = ticket.data_ptr() if ticket is not None else 0
     if config.get("memo", True):
         # id -> distance memo of each row in flight (scratch; the kernel clears a row's slice)
         smem, warps, blocks = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
