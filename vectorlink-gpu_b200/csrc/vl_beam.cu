@@ -349,29 +349,6 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                 __syncwarp();
                 vl_key_t* t = vq; vq = vq_n; vq_n = t;
             }
-#ifdef VL_NEXT_PF
-            // The nodes now at the head of the visit queue are the likely pops of the next iteration:
-            // start their graph rows on the way.
-            {
-                const int lpn = (wb * 4 + 127) / 128 + 1;
-#pragma unroll 1
-                for (int l = lane; l < pvc * lpn; l += 32) {
-                    const int v = l / lpn;
-                    const int32_t node = vl_key_id(vq[v]);
-                    if (node != VL_MAXINT && node >= 0 && (int64_t)node < p.n) {
-                        const char* r0 = reinterpret_cast<const char*>(p.graph + (int64_t)node * wb);
-                        const char* a = r0 - ((uintptr_t)r0 & 127) + (l - v * lpn) * 128;
-                        if (a < r0 + wb * 4) {
-#if VL_NEXT_PF == 2
-                            asm volatile("prefetch.global.L1 [%0];" : : "l"(a));
-#else
-                            asm volatile("prefetch.global.L2 [%0];" : : "l"(a));
-#endif
-                        }
-                    }
-                }
-            }
-#endif
             VL_PHASE(0);   // pop
             // ---- neighbour ids of the popped nodes (kernels.py:244), then which of them need a
             // gather: live ids the memo does not know.  VL_PB chunks of 32 candidates per round so
