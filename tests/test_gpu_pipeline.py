@@ -113,6 +113,10 @@ CASES = [
     ("readahead-hits-k_none", 1200, 16, 6, 6, 40, {"visit_queue_factor": 1, "exclude_factor": 6}),
     ("seen-not-multiple-of-pvc", 1200, 24, 7, 7, 20, {"parallel_visit_count": 3, "exclude_factor": 5}),
     ("no-seen-list", 800, 16, 8, 8, 10, {"exclude_factor": 0}),
+    ("dim256", 500, 256, 8, 8, 7, {}),
+    ("dim384", 400, 384, 8, 8, 6, {}),
+    ("dim512", 400, 512, 8, 8, 6, {}),
+    ("dim768", 300, 768, 8, 8, 5, {}),
     ("dim1024", 400, 1024, 8, 8, 6, {}),
     ("dim1536", 300, 1536, 8, 8, 4, {}),
 ]
