@@ -57,3 +57,12 @@ def test_cpu_tensors_are_refused_not_computed_on_the_host(built_lib):
     v = torch.zeros(4, 8)
     with pytest.raises(_lib.VlError):
         calculate_distances(v, torch.zeros(4, 2, dtype=torch.int32))
+
+
+def test_connected_components_rejects_bad_shapes_without_touching_the_gpu(built_lib):
+    from vectorlink_gpu import _lib
+    lib = _lib.lib()
+    assert lib.vl_connected_components(None, None, 1 << 31, 4, 4, ctypes.c_float(0.5), None, None, None) != 0
+    assert b"int32" in lib.vl_last_error()
+    assert lib.vl_connected_components(None, None, 10, 4, 2, ctypes.c_float(0.5), None, None, None) != 0   # ld < w
+    assert lib.vl_connected_components(None, None, 0, 4, 4, ctypes.c_float(0.5), None, None, None) == 0     # no nodes: nothing to do
