@@ -168,6 +168,23 @@ def test_distance_memo_changes_nothing(built_lib):
     assert np.array_equal(results[0], results[1])
 
 
+def test_memo_decision_of_the_build_changes_nothing(built_lib):
+    """generate_ann switches the memo off for later rounds when its self-recall check gathered nearly
+    every candidate; whichever way it decides, the graph equals the one built with the memo forced
+    on or off."""
+    from vectorlink_gpu.ann import generate_ann
+    rng = np.random.default_rng(91)
+    vectors = t(unit(rng, 5000, 32))
+    cfg = oracle.make_config(beam_size=8, batch_size=1000)
+    graphs = []
+    for extra in ({}, {"memo": True}, {"memo": False}):
+        b, d = generate_ann(vectors, dict(cfg, **extra))
+        assert isinstance(generate_ann.memo_useful, bool)
+        graphs.append((n(b), n(d)))
+    for b, d in graphs[1:]:
+        assert np.array_equal(b, graphs[0][0]) and np.array_equal(d, graphs[0][1])
+
+
 def test_row_schedule_changes_nothing(built_lib):
     """More rows than the launch keeps in flight: warps that draw their next row from the shared
     counter and warps on a fixed stride produce the same queues, equal to the oracle's."""

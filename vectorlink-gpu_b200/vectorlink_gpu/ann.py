@@ -68,8 +68,10 @@ def loop_bounds(config: Dict) -> Tuple[int, int, int]:
 
 
 def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
-                 config, n_iters, dump_last, exclude, self_base, group_rows, flags, full):
+                 config, n_iters, dump_last, exclude, self_base, group_rows, flags, full, stats=None):
     pvc = config["parallel_visit_count"]
+    if stats is None:
+        stats = STATS
     vq_len = config["visit_queue_factor"] * config["beam_size"]
     p = BeamParams()
     p.vectors = vectors.data_ptr()
@@ -106,8 +108,8 @@ def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len
     p.memo = 0
     p.memo_entries = 0
     p.memo_slots = 0
-    p.stats = STATS.data_ptr() if STATS is not None else 0
-    p.flags = 1 if (STATS is not None and STATS_TIMERS) else 0
+    p.stats = stats.data_ptr() if stats is not None else 0
+    p.flags = 1 if (stats is not None and stats is STATS and STATS_TIMERS) else 0
     # rows differ in the work they take: warps draw their next row from a counter instead of a fixed stride
     ticket = torch.zeros(1, dtype=torch.int64, device=vectors.device) if config.get("row_ticket", True) else None
     p.row_ticket = ticket.data_ptr() if ticket is not None else 0
@@ -177,10 +179,19 @@ def _fused_batches(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_l
     full = torch.zeros((max(groups, 1),), dtype=torch.int32, device=dev)
     if rows == 0:
         return []
+    # a caller that wants to know how useful the distance memo is on this graph (generate_ann's
+    # self-recall check) gets the share of candidates that had to be gathered
+    counters = None
+    if config.get("measure_gathered") and config.get("memo", True) and STATS is None:
+        counters = torch.zeros(24, dtype=torch.int64, device=dev)
     _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
-                 config, n_max, False, exclude, self_base, group_rows, flags, full)
+                 config, n_max, False, exclude, self_base, group_rows, flags, full, counters)
     flags_h = flags.cpu().tolist()
     full_h = full.cpu().tolist()
+    if counters is not None:
+        c = counters.cpu().tolist()
+        offered = c[7] * config["parallel_visit_count"] * graph.size(1)
+        _fused_batches.last_gathered = c[1] / offered if offered else None
     counts = []
     for gi in range(groups):
         lo, hi = gi * group_rows, min(rows, (gi + 1) * group_rows)
@@ -204,6 +215,14 @@ def _fused_batches(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_l
         out_ids[lo:hi, :out_cols].copy_(tmp_i[:, :out_cols])
         out_dist[lo:hi, :out_cols].copy_(tmp_d[:, :out_cols])
     return counts
+
+
+_fused_batches.last_gathered = None
+
+# Above this share of gathered candidates the distance memo costs more than it saves (measured on
+# 1M x 96 with 98 % gathered: build round 28 % and search 9 % faster without it; on 1M x 128 with
+# 5-25 % gathered the memo is what makes the round 2.5 x faster).
+MEMO_USELESS_ABOVE = 0.75
 
 
 def closest_vectors_stepwise(query_vecs: Tensor, search_queue: Queue, vectors: Tensor, beams: Tensor, config: Dict,
@@ -337,6 +356,7 @@ def generate_ann(vectors: Tensor, config: Dict, group=None) -> Tuple[Tensor, Ten
                       for lo, hi in partition_rows(n_batches, world)]
             row_lo, row_hi = bounds[rank]
     loops_run = 0
+    memo_useful = True
     for i in range(0, config["optimization_loops"]):
         print_timestamp(f"start of cagra loop {i}")
         next_beams = torch.empty_like(beams)
@@ -353,9 +373,10 @@ def generate_ann(vectors: Tensor, config: Dict, group=None) -> Tuple[Tensor, Ten
             return n
 
         round_config = config
-        if i == 0 and "memo" not in config and "memo_entries" not in config:
+        if (i == 0 or not memo_useful) and "memo" not in config and "memo_entries" not in config:
             # the circulant start graph makes candidates that hardly ever repeat within a row
-            # (6 % memo hits measured): the first round runs faster without the memo
+            # (6 % memo hits measured): the first round runs faster without the memo; so do later
+            # rounds on data where the last self-recall check gathered nearly every candidate
             round_config = dict(config, memo=False)
         if row_hi > row_lo:
             if fused:
@@ -376,16 +397,21 @@ def generate_ann(vectors: Tensor, config: Dict, group=None) -> Tuple[Tensor, Ten
             (beams, beam_distances) = (next_beams, next_beam_distances)
         loops_run += 1
         prefix = min(num_vecs, 1000)
-        (found, recall) = ann_calculate_recall(vectors, beams.narrow_copy(1, 0, beam_size), config,
-                                               sample=vectors[:prefix])
+        _fused_batches.last_gathered = None
+        (found, recall) = ann_calculate_recall(vectors, beams.narrow_copy(1, 0, beam_size),
+                                               dict(config, measure_gathered=True), sample=vectors[:prefix])
+        if _fused_batches.last_gathered is not None:
+            memo_useful = _fused_batches.last_gathered <= MEMO_USELESS_ABOVE
         if recall == 1.0:
             break
         print_timestamp(f"end of cagra loop {i}")
     generate_ann.last_loops = loops_run
+    generate_ann.memo_useful = memo_useful
     return (beams.narrow_copy(1, 0, beam_size), beam_distances.narrow_copy(1, 0, beam_size))
 
 
 generate_ann.last_loops = 0
+generate_ann.memo_useful = True
 
 
 def initial_queue(vectors: Tensor, config: Dict):
@@ -529,6 +555,10 @@ class ANN:
                 self.distances = distances
         else:
             (self.beams, self.distances) = generate_ann(self.vectors, self.configuration, group=group)
+            if not generate_ann.memo_useful and "memo" not in self.configuration:
+                # the last self-recall check over this graph gathered nearly every candidate:
+                # searches run faster without the distance memo (same results either way)
+                self.configuration["memo"] = False
         if symmetrize:
             from .kernels import symmetrize as _symmetrize
             (self.beams, self.distances) = _symmetrize(self.vectors, self.beams.contiguous(), self.distances.contiguous(),
