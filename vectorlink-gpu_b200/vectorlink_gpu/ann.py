@@ -182,13 +182,16 @@ def _fused_batches(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_l
     # a caller that wants to know how useful the distance memo is on this graph (generate_ann's
     # self-recall check) gets the share of candidates that had to be gathered
     counters = None
-    if config.get("measure_gathered") and config.get("memo", True) and STATS is None:
+    if config.get("measure_gathered") and config.get("memo", True):
         counters = torch.zeros(24, dtype=torch.int64, device=dev)
     _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
                  config, n_max, False, exclude, self_base, group_rows, flags, full, counters)
     flags_h = flags.cpu().tolist()
     full_h = full.cpu().tolist()
     if counters is not None:
+        if STATS is not None:
+            shared = min(STATS.numel(), counters.numel())
+            STATS[:shared].add_(counters[:shared])
         c = counters.cpu().tolist()
         offered = c[7] * config["parallel_visit_count"] * graph.size(1)
         _fused_batches.last_gathered = c[1] / offered if offered else None
