@@ -6,9 +6,12 @@ One "step" is one complete graph build (`ANN(vectors=...)`: circulant start grap
 `optimization_loops` rounds of fused beam search + prune + self-recall check) over the
 workload's synthetic vectors.  The JSON line reports build vectors/s (`value`, inputs already
 in HBM; `e2e` with host buffers), the search QPS and recall@10 of the built graph, the
-roofline of the dominant kernel, and a CPU baseline (the C oracle on a bounded sample).
+roofline of the dominant kernel (per launch class: the first build round, the later rounds, the
+search), and a CPU baseline (the C oracle on a bounded sample).
 `--impl reference` times the reference's algorithm on the host cores only (the C oracle, all
-threads) on a bounded sample of the same workload.
+threads) on a bounded sample of the same workload.  The reference's own Numba kernels are not run
+on the GPU: below 1024 dimensions they read shared memory past what was written or allocated
+(kernels.py:50-69,217,231) and after a prune they index vectors[MAXINT] (kernels.py:245-247).
 """
 from __future__ import annotations
 
@@ -36,10 +39,14 @@ WORKLOADS = {
     "c2": dict(n=1_000_000, dim=128, metric="l2", degree=32, beam=64, queries=10_000, kind="sift_like", centres=256),
     # config 3: 1,000,000 x 768 unit-norm embedding-like mixture, cosine, degree 64, beam 128
     "c3": dict(n=1_000_000, dim=768, metric="cosine", degree=64, beam=128, queries=10_000, kind="embed_like",
-               centres=1000, noise=0.1),
+               centres=1000, noise=0.1, unit_centres=True),
     # config 4 (per-GPU shard of it at N GPUs): 10,000,000 x 96 Deep-like, cosine, degree 32
+    # (centres are plain N(0,1) draws, norm ~ 9.8, not normalised; only the rows are)
     "c4": dict(n=10_000_000, dim=96, metric="cosine", degree=32, beam=64, queries=10_000, kind="embed_like",
-               centres=4096, noise=0.3),
+               centres=4096, noise=0.3, unit_centres=False),
+    # config 5 (20,000,000 x 1024 over 8 GPUs): cosine, degree 64, beam 128, 100,000 queries
+    "c5": dict(n=20_000_000, dim=1024, metric="cosine", degree=64, beam=128, queries=100_000, kind="embed_like",
+               centres=16384, noise=0.05, unit_centres=True),
 }
 
 
@@ -79,7 +86,9 @@ def make_data(w, n, device, seed=0, queries=None):
     if w["kind"] == "sift_like":
         centres = torch.rand((w["centres"], dim), device=device, generator=g) * 255.0
     elif w["kind"] == "embed_like":
-        centres = torch.nn.functional.normalize(torch.randn((w["centres"], dim), device=device, generator=g), dim=1)
+        centres = torch.randn((w["centres"], dim), device=device, generator=g)
+        if w.get("unit_centres", True):
+            centres = torch.nn.functional.normalize(centres, dim=1)
     vectors = draw(n)
     q = draw(nq)
     return vectors.contiguous(), q.contiguous()
@@ -155,6 +164,9 @@ def oracle_build_rate(w, sample_n, seed=0):
     """The C oracle (all host threads) building the graph of a `sample_n`-vector draw of the
     workload with the same ANN parameters; returns (vectors/s, seconds, loops, threads)."""
     import oracle
+    # a launcher that starts several workers per node exports OMP_NUM_THREADS=1 to each of them;
+    # this leg runs on one rank only and is meant to use the host's cores
+    oracle.set_num_threads(os.cpu_count() or 1)
     vec, _ = make_data(w, sample_n, "cpu", seed, queries=1)
     kw = ann_kwargs(w)
     metric = kw.pop("metric")
@@ -166,31 +178,116 @@ def oracle_build_rate(w, sample_n, seed=0):
     return sample_n / dt, dt, loops, oracle.num_threads()
 
 
+def default_sample(w):
+    """Vectors in the CPU sample: about 10-30 s of oracle work on 16-32 host cores."""
+    return max(500, min(w["n"], int(2_000_000 / (w["dim"] * (w["degree"] / 16)))))
+
+
 def run_reference(args, w, name):
-    """The reference's CPU implementation of the path (the C restatement; the Numba kernels
-    themselves simulate at about one CUDA block per second) on a bounded sample."""
+    """The reference's CPU implementation of the path on the host cores: the C restatement of its
+    algorithm (oracle/), OpenMP over all cores, building the graph of a bounded sample of the
+    workload.  (The reference's own kernels exist only as Numba CUDA kernels: the Numba simulator
+    runs them at about one CUDA block per second, and on the GPU they read out of range below 1024
+    dimensions, see the module docstring - neither is a usable timing arm.)"""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = args.sample or max(500, min(w["n"], int(2_000_000 / (w["dim"] * (w["degree"] / 16)))))
-    rates = []
-    for _ in range(args.warmup):
+    sample = args.sample or default_sample(w)
+    budget_s = 240.0                       # the whole arm ends within a few minutes
+    t_begin = time.time()
+    for _ in range(min(args.warmup, 1)):
         oracle_build_rate(w, min(sample, 500))
-    t_all = time.time()
-    for _ in range(args.steps):
+    rates, secs = [], []
+    for i in range(args.steps):
         rate, dt, loops, threads = oracle_build_rate(w, sample)
         rates.append(rate)
-    ms = (time.time() - t_all) / max(1, args.steps) * 1e3
+        secs.append(dt)
+        if time.time() - t_begin + dt > budget_s:      # no room for another step of this length
+            break
+    ms = float(np.mean(secs)) * 1e3
     value = float(np.mean(rates))
     line = {"impl": "reference", "metric": "graph_build_vectors_per_s", "value": value, "unit": "vectors/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "n_gpus": args.gpus, "steps": len(rates), "warmup": min(args.warmup, 1), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": name, "sample_vectors": sample, **{k: v for k, v in ann_kwargs(w).items()}},
             "cpu_baseline": {"value": value, "unit": "vectors/s", "cores": threads, "kind": "port",
                              "sample": f"full build of a {sample}-vector draw of {name} ({loops} loops), C oracle with OpenMP"},
             "e2e": {"value": value, "unit": "vectors/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+            "gpu_launches": 0,
+            "numba_on_gpu": "not run: the reference's kernels read shared memory out of range for dim < 1024 "
+                            "(kernels.py:217,231) and index vectors[MAXINT] after a prune (kernels.py:245-247)"}
     print(json.dumps(line), flush=True)
+
+
+def launch_classes(profile, reps, dim):
+    """Fused-kernel launches of a timed region grouped by phase (first build round / later build
+    rounds / self-recall check / search), each with its mean duration (CUDA events recorded around
+    the launch on the launching stream), the distance evaluations the reference's schedule
+    prescribes and the candidate rows the kernel actually loaded (its own counter)."""
+    bytes_per_row = 4 * dim + 12          # candidate row + neighbour id + (id, distance) result
+    groups = {}
+    for p in profile:
+        tag = p.get("tag", "search")
+        cls = "build_round0" if tag == "round0" else ("build_later_rounds" if tag.startswith("round") else tag)
+        groups.setdefault(cls, []).append(p)
+    out = {}
+    for cls, ps in groups.items():
+        ms = sum(p["start"].elapsed_time(p["end"]) for p in ps)
+        evals = sum(p["evals"] for p in ps)
+        gathered = sum(int(p["stats"][1].item()) for p in ps if p.get("stats") is not None)
+        out[cls] = {"launches_per_step": len(ps) / reps, "ms_per_launch": ms / len(ps),
+                    "evals_per_launch": evals / len(ps), "gathered_rows_per_launch": gathered / len(ps),
+                    "gathered_fraction": gathered / evals if evals else None,
+                    "memo": all(p["memo"] for p in ps),
+                    "schedule_gbs": evals * bytes_per_row / (ms * 1e-3) / 1e9 if ms else None,
+                    "gathered_gbs": gathered * bytes_per_row / (ms * 1e-3) / 1e9 if ms else None}
+    return out
+
+
+def dram_captures(workload):
+    """ncu DRAM counters of earlier captures of this workload, kept as data beside the summaries."""
+    try:
+        doc = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))
+        return [c for c in doc["captures"] if c["workload"] == workload]
+    except Exception:
+        return []
+
+
+def roofline_of(build_classes, search_classes, peak, peak_kind, workload, dim, kernel_share):
+    """Three figures per launch class, all against the measured HBM copy bandwidth:
+    `vs_reference_schedule` - bytes the reference's schedule would move (every evaluation gathers
+        its row), per second: can exceed 1 because the kernel memoises distances per query row;
+    `gathered` - bytes of the candidate rows the kernel really loaded, per second: the achieved
+        bandwidth of the gather, whichever level of the memory system served it;
+    `dram` - DRAM bytes of an ncu capture of the same launch class (scaled by gathered rows).
+    The headline `achieved`/`frac` is `gathered` of the build's later rounds, whose rows come from
+    DRAM; the first round's candidates lie in a band of rows that stays in L2, so its `gathered`
+    figure is an L2 rate and is reported but not used as the HBM fraction."""
+    classes = {}
+    caps = dram_captures(workload)
+    for cls, c in list(build_classes.items()) + [("search", search_classes.get("search"))]:
+        if not c:
+            continue
+        entry = dict(c)
+        entry["vs_reference_schedule"] = c["schedule_gbs"] / peak if c["schedule_gbs"] else None
+        entry["gathered_frac"] = c["gathered_gbs"] / peak if c["gathered_gbs"] else None
+        for cap in caps:
+            if cap["class"] == cls and bool(cap["memo"]) == bool(c["memo"]):
+                traffic = cap["dram_bytes_per_gathered_row"] * c["gathered_rows_per_launch"]
+                entry["dram_traffic_bytes"] = traffic
+                entry["dram_gbs"] = traffic / (c["ms_per_launch"] * 1e-3) / 1e9
+                entry["dram_frac"] = entry["dram_gbs"] / peak
+                entry["dram_capture"] = {k: cap[k] for k in ("commit", "summary") if k in cap}
+        classes[cls] = entry
+    head = classes.get("build_later_rounds") or classes.get("build_round0") or {}
+    served = "DRAM" if "build_later_rounds" in classes else "mostly L2 (single-round build: circulant band)"
+    return {"bound": "hbm", "kernel": "beam_search_kernel", "class": "build_later_rounds" if "build_later_rounds" in classes else "build_round0",
+            "achieved": head.get("gathered_gbs"), "peak": peak, "unit": "GB/s",
+            "frac": (head.get("gathered_gbs") or 0.0) / peak, "peak_source": peak_kind,
+            "frac_of_8TBs_nominal": (head.get("gathered_gbs") or 0.0) / 8000.0,
+            "achieved_counts": "bytes of candidate rows actually loaded (kernel counter) x (4*dim+12) / CUDA-event time",
+            "rows_served_from": served, "bytes_per_row": 4 * dim + 12,
+            "traffic": head.get("dram_traffic_bytes"), "kernel_share_of_step": kernel_share, "classes": classes}
 
 
 def main():
@@ -282,7 +379,6 @@ def main():
     if rank == 0:
         sampler.start()
     vl_ann.PROFILE = []
-    vl_ann.STATS = torch.zeros(16, dtype=torch.int64, device=dev)    # work counters of the fused kernel
     launches0 = _lib.LAUNCHES
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -294,21 +390,11 @@ def main():
     launches = _lib.LAUNCHES - launches0
     profile = vl_ann.PROFILE
     vl_ann.PROFILE = None
-    build_stats = vl_ann.STATS.cpu().tolist()
-    vl_ann.STATS = None
     ms_total = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else None
 
-    # the dominant kernel: the fused beam search over all rows (one launch per build round)
-    k_ms = [p["start"].elapsed_time(p["end"]) for p in profile]
-    k_evals = [p["evals"] for p in profile]
-    big = [i for i, p in enumerate(profile) if p["rows"] >= min(n, 10_000)]
-    bytes_per_eval = 4 * dim + 12
-    if big:
-        ach = sum(k_evals[i] for i in big) * bytes_per_eval / (sum(k_ms[i] for i in big) * 1e-3) / 1e9
-        kernel_share = sum(k_ms) / ms_total
-    else:
-        ach, kernel_share = 0.0, 0.0
+    build_classes = launch_classes(profile, args.steps, dim)
+    kernel_share = sum(p["start"].elapsed_time(p["end"]) for p in profile) / ms_total if profile else 0.0
 
     # end to end with host buffers
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -342,8 +428,7 @@ def main():
     sprof = vl_ann.PROFILE
     vl_ann.PROFILE = None
     search_ms = s0.elapsed_time(s1) / reps
-    s_k_ms = sum(p["start"].elapsed_time(p["end"]) for p in sprof) / reps
-    s_evals = sum(p["evals"] for p in sprof) / reps
+    search_classes = launch_classes(sprof, reps, dim)
     recall = graph_recall = None
     if not args.quick:
         index = ann.index if world > 1 else ann
@@ -380,34 +465,17 @@ def main():
                     "h2d_bytes_per_step": total * dim * 4, "d2h_bytes_per_step": total * kw["beam_size"] * 8},
             "gpu_launches": launches,
             "search": {"qps": queries.size(0) / (search_ms * 1e-3), "queries": queries.size(0), "k": 10,
-                       "recall_at_10": recall, "ms": search_ms,
-                       "kernel_gbs": (s_evals * bytes_per_eval / (s_k_ms * 1e-3) / 1e9) if s_k_ms else None},
+                       "recall_at_10": recall, "ms": search_ms},
             "graph_recall_at_10": graph_recall,
-            "roofline": {"bound": "hbm", "kernel": "beam_search_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
-                         "frac": ach / peak, "peak_source": peak_kind, "frac_of_8TBs_nominal": ach / 8000.0,
-                         "bytes_per_eval": bytes_per_eval, "evals_per_launch": k_evals[big[0]] if big else 0,
-                         "launch_ms": (sum(k_ms[i] for i in big) / len(big)) if big else None,
-                         "kernel_share_of_step": kernel_share, "traffic": None,
-                         "gathered_fraction": (build_stats[1] / max(1, sum(k_evals))),
-                         "gathered_gbs": (build_stats[1] * bytes_per_eval / (sum(k_ms) * 1e-3) / 1e9) if k_ms else None,
-                         "note": "achieved counts every distance evaluation of the reference's schedule; the kernel "
-                                 "memoises distances per row and gathers only gathered_fraction of them"},
+            "roofline": roofline_of(build_classes, search_classes, peak, peak_kind, name, dim, kernel_share),
             "clocks": clocks, "status_word": status,
         }
         if not args.no_cpu_baseline and world == 1:
-            sample = args.sample or max(500, min(n, int(2_000_000 / (dim * (kw["beam_size"] / 16)))))
+            sample = args.sample or default_sample(w)
             rate, dt, loops, threads = oracle_build_rate(w, sample)
             line["cpu_baseline"] = {"value": rate, "unit": "vectors/s", "cores": threads, "kind": "port",
                                     "sample": f"full build of a {sample}-vector draw of {name} ({loops} loops, {dt:.1f} s), "
                                               "C oracle with OpenMP"}
-        # measured DRAM bytes per evaluation of this kernel on this workload (ncu summary in profiles/)
-        traffic_file = os.path.join(ROOT, "profiles", f"beam_search_kernel_{name}_dram_traffic.md")
-        if os.path.exists(traffic_file) and big:
-            import re
-            m = re.search(r"^dram_bytes_per_eval:\s*([0-9.]+)", open(traffic_file).read(), re.M)
-            if m:
-                line["roofline"]["traffic"] = float(m.group(1)) * k_evals[big[0]]
-                line["roofline"]["traffic_source"] = os.path.relpath(traffic_file, ROOT)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

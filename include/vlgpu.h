@@ -96,7 +96,10 @@ int vl_seen_add(int32_t* seen, int64_t b, int e, const int32_t* visit, int v, in
  * so e <= VL_SEEN_NOALLOC_MAX_WIDTH; wider lists are rejected with an error.  Calls nothing
  * that allocates.  Same results as vl_seen_add.  All calls on a GPU share the array: calls
  * that overlap on the GPU race, keep them stream-ordered.  The first call on a device looks up
- * the array's address and should happen before any stream capture begins. */
+ * the array's address and should happen before any stream capture begins.  The address is kept
+ * per device for the life of the process: after a cudaDeviceReset (or any teardown of the
+ * device's primary context) it is stale and this entry point must not be used again in that
+ * process. */
 #define VL_SEEN_NOALLOC_MAX_WIDTH 4096
 int vl_seen_add_noalloc(int32_t* seen, int64_t b, int e, const int32_t* visit, int v, int* first_out, void* stream);
 
@@ -108,6 +111,13 @@ int vl_seen_add_noalloc(int32_t* seen, int64_t b, int e, const int32_t* visit, i
  * outputs [n, out_cols].  Inputs are not modified.  w <= 2048. */
 int vl_prune(const int32_t* beams, const float* dist, int64_t n, int w, int do_punch, int32_t* beams_out,
              float* dist_out, int out_cols, int* status, void* stream);
+
+/* vl_prune over the rows [row_lo, row_hi) only: rows outside the range are still read (a row's
+ * detour witnesses live in its neighbours' rows) but only rows of the range are written, at
+ * their own row index of the [n, out_cols] outputs.  A build whose rows are split across
+ * several GPUs prunes each GPU's share with it (the reference is single-device: constants.py:7). */
+int vl_prune_rows(const int32_t* beams, const float* dist, int64_t n, int w, int64_t row_lo, int64_t row_hi,
+                  int do_punch, int32_t* beams_out, float* dist_out, int out_cols, int* status, void* stream);
 
 /* Reverse edges (the reference only sketches them: symmetrize_beams, kernels.py:503-550, is dead
  * code): out[y, 0..keep) = the nodes x that list y among the first `scan` columns of beams [n, d],
@@ -173,6 +183,9 @@ typedef struct vl_beam_params {
     int32_t reserved;
     unsigned long long* row_ticket; /* optional device counter, zero at launch: warps then draw their next row from it
                                   (rows that take unequal time no longer wait for a fixed partner); NULL = fixed stride */
+    int64_t group_row0;        /* row 0 of this launch sits at this position of the reference's host loop: its batch
+                                  (the row of both flag arrays) is (group_row0 + row) / group_rows.  0 for a launch
+                                  that starts on a batch boundary */
 } vl_beam_params;
 
 int vl_beam_search(const vl_beam_params* params, void* stream);

@@ -81,6 +81,12 @@ def num_threads() -> int:
     return int(lib().vlo_num_threads())
 
 
+def set_num_threads(threads: int) -> int:
+    """Use `threads` OpenMP threads from now on, whatever OMP_NUM_THREADS said at start-up."""
+    lib().vlo_set_num_threads(ctypes.c_int(int(threads)))
+    return num_threads()
+
+
 def primes_table(count: int = 965) -> np.ndarray:
     """The reference's seed table (constants.py:10-980), regenerated rather than copied:
     the 584 consecutive primes from 10,000,349, the 75 consecutive primes from 1,009,007,

@@ -592,3 +592,14 @@ int vlo_num_threads(void)
     return 1;
 #endif
 }
+
+/* Threads for the parallel loops from here on (a launcher may have exported OMP_NUM_THREADS=1
+ * for its worker processes; a timing run wants the host's cores regardless). */
+void vlo_set_num_threads(int threads)
+{
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}

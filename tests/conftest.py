@@ -38,6 +38,13 @@ def small():
 
 
 @pytest.fixture(scope="session")
+def multi():
+    """A three-round build by the reference's host code with two one-token repairs (the carried
+    distances, stable final sorts): see make_golden.make_multi."""
+    return dict(np.load(os.path.join(GOLDEN, "multi_host.npz")))
+
+
+@pytest.fixture(scope="session")
 def built_lib():
     """libvlgpu.so, compiled on demand (nvcc cross-compiles without a GPU)."""
     sys.path.insert(0, PKG_ROOT)

@@ -1,9 +1,9 @@
 """Generates the golden fixtures in this directory from the reference's own code.
 
-Run in the development container (where the reference tree is mounted read-only):
+Needs a checkout of the reference (read only), named by VL_REFERENCE_ROOT:
 
-    python tests/golden/make_golden.py sim    # -> kat_sim.npz   (a few minutes)
-    python tests/golden/make_golden.py host   # -> c1_host.npz, small_host.npz
+    VL_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py sim    # -> kat_sim.npz   (a few minutes)
+    VL_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py host   # -> c1_host.npz, small_host.npz, multi_host.npz
 
 ``sim``  runs the reference's real Numba kernels in the Numba CUDA simulator on micro-cases
          (about one second per simulated block, so only tens of blocks per case).
@@ -271,6 +271,64 @@ def make_host():
     print(f"small: build {float(res2['build_seconds']):.1f}s self-recall {int(res2['self_recall_found'])}", flush=True)
     np.savez_compressed(os.path.join(HERE, "small_host.npz"), **res2)
     print("wrote small_host.npz")
+    make_multi(ref)
+
+
+def make_multi(ref):
+    """A build that needs several rounds, from the PATCHED reference -> multi_host.npz.
+
+    As shipped, generate_ann never rebinds `beam_distances` (ann.py:172 assigns prune_'s second
+    result to an unused name), so a second round would pair the new neighbour lists with the
+    first round's circulant distances.  Both c1 and small reach self-recall 1.0 in round one and
+    never get there.  Here the one name at that statement (and at its no-prune twin, ann.py:174)
+    is changed in the function's text in memory - nothing else - so that rounds two and three run
+    on consistent lists: pruned rows with MAXINT tails, re-seeding with carried distances."""
+    import inspect
+    import torch
+    A = ref.ann
+    src = inspect.getsource(A.generate_ann)
+    assert src.count("(beams, distances) = ") == 2
+    exec(compile(src.replace("(beams, distances) = ", "(beams, beam_distances) = "), "<patched generate_ann>", "exec"),
+         A.__dict__)
+    # Second patch, same style: the last sort of punchout_duplicates_ (kernels.py:402) and of prune_
+    # (kernels.py:466) is torch's default, which is not stable; among entries at exactly the same
+    # distance it may undo the (distance, id) order index_sort established, differently per torch
+    # build and device (seen on this CPU: two ids at one distance swap, the "head changed" test
+    # fires, the loop runs 25 iterations instead of 10).  `stable=True` there makes the tie order
+    # the one index_sort defines, which is also what the oracle and the CUDA path implement.
+    K = ref.kernels
+    for name in ("punchout_duplicates_", "prune_"):
+        fsrc = inspect.getsource(getattr(K, name))
+        assert fsrc.count("distances.sort()") == 1
+        exec(compile(fsrc.replace("distances.sort()", "distances.sort(stable=True)"), f"<patched {name}>", "exec"),
+             K.__dict__)
+        for mod in (ref.queue, ref.utils, ref.ann):
+            if hasattr(mod, name):
+                setattr(mod, name, getattr(K, name))
+    rounds = []
+    stamp = A.print_timestamp
+    A.print_timestamp = lambda msg: rounds.append(msg) if str(msg).startswith("start of cagra loop") else None
+    rng = np.random.default_rng(17)
+    dim, count = 48, 1800
+    centres = rng.uniform(0, 255, (12, dim))
+    pts = centres[rng.integers(0, 12, count)] + rng.normal(0, 20, (count, dim))
+    v = np.round(pts).clip(0, 255).astype(np.float32)
+    v = (v / np.linalg.norm(v, axis=1, keepdims=True)).astype(np.float32)
+    kwargs = dict(beam_size=8, visit_queue_factor=2, recall_search_queue_factor=2, batch_size=500)
+    t0 = time.time()
+    ann = A.ANN(torch.from_numpy(v), **kwargs)
+    A.print_timestamp = stamp
+    res = {"vectors": v, "beams": ann.beams.numpy().copy(), "distances": ann.distances.numpy().copy(),
+           "loops": np.int64(len(rounds))}
+    for k, val in kwargs.items():
+        res[f"cfg_{k}"] = np.int64(val)
+    found, _ = ann.recall()
+    res["self_recall_found"] = np.int64(found)
+    assert np.array_equal(res["distances"], ref.kernels.calculate_distances(torch.from_numpy(v), ann.beams).numpy())
+    print(f"multi: {len(rounds)} rounds in {time.time() - t0:.1f}s, self-recall {found}", flush=True)
+    assert len(rounds) >= 2, "the case must not converge in one round"
+    np.savez_compressed(os.path.join(HERE, "multi_host.npz"), **res)
+    print("wrote multi_host.npz")
 
 
 if __name__ == "__main__":
@@ -279,3 +337,5 @@ if __name__ == "__main__":
         make_sim()
     if what in ("host", "all"):
         make_host()
+    if what == "multi":
+        make_multi(load_reference("host"))

@@ -1,7 +1,7 @@
 """Loads the read-only reference package on a CPU-only machine (fixture generation only).
 
-Used by ``make_golden.py`` in the development container, where the reference tree is
-mounted; nothing in the test-suite imports this at run time.
+Used by ``make_golden.py`` on a machine that has a checkout of the reference
+(``VL_REFERENCE_ROOT`` names it); nothing in the test-suite imports this at run time.
 
 The reference cannot be imported without a GPU as shipped: ``constants.py`` builds its
 prime table with ``device="cuda"``, ``ann.py`` imports ``datafusion`` (not installed),
@@ -27,7 +27,8 @@ import sys
 import threading
 import types
 
-REFERENCE_ROOT = os.environ.get("VL_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
+REFERENCE_ROOT = os.environ.get("VL_REFERENCE_ROOT")
+
 
 
 def _parse_constants(path):
@@ -42,6 +43,8 @@ def _parse_constants(path):
 
 def load_reference(mode: str):
     assert mode in ("simulator", "host")
+    if not REFERENCE_ROOT or not os.path.isdir(os.path.join(REFERENCE_ROOT, "vectorlink_gpu")):
+        raise RuntimeError("set VL_REFERENCE_ROOT to a checkout of vectorlink-ai/vectorlink-gpu")
     os.environ["NUMBA_ENABLE_CUDASIM"] = "1"
     import numpy as np
     import torch

@@ -33,6 +33,30 @@ def main():
     assert np.array_equal(ids.cpu().numpy(), g["search_tree_ids"]), "data-parallel search differs"
     assert np.array_equal(dd.cpu().numpy(), g["search_tree_dist"])
 
+    # three rounds whose batches straddle the two ranks' row ranges (1800 rows, batches of 500):
+    # the reference's host code with its two accidental spots repaired (tests/golden/make_golden.py)
+    m = dict(np.load(os.path.join(ROOT, "tests", "golden", "multi_host.npz")))
+    mkw = {k[4:]: int(v) for k, v in m.items() if k.startswith("cfg_")}
+    mv = torch.from_numpy(m["vectors"]).to(dev)
+    mlo, mhi = partition_rows(mv.size(0), world)[rank]
+    three = ShardedANN(mv[mlo:mhi].contiguous(), mode="rows", **mkw)
+    assert np.array_equal(three.index.beams.cpu().numpy(), m["beams"]), "three-round row-parallel graph differs"
+    assert np.array_equal(three.index.distances.cpu().numpy(), m["distances"])
+
+    # batches of a few rows stop early inside the build (the reference's batch-wide check); a batch
+    # that straddles the ranks must take the same decision on both: against the CPU oracle
+    import oracle
+    rng = np.random.default_rng(123)
+    tv = rng.standard_normal((250, 24)).astype(np.float32)
+    tv /= np.linalg.norm(tv, axis=1, keepdims=True)
+    for batch in (3, 7, 60):
+        tkw = dict(beam_size=6, batch_size=batch, optimization_loops=2)
+        wb, wd, _, _ = oracle.generate_ann(tv, oracle.make_config(**tkw))
+        tlo, thi = partition_rows(250, world)[rank]
+        tiny = ShardedANN(torch.from_numpy(tv[tlo:thi]).to(dev), mode="rows", **tkw)
+        assert np.array_equal(tiny.index.beams.cpu().numpy(), wb), f"batch_size {batch}: graph differs from the oracle"
+        assert np.array_equal(tiny.index.distances.cpu().numpy(), wd)
+
     # mode "shards": local graphs + cross-shard merge; quality check against brute force
     shards = ShardedANN(vectors[lo:hi].contiguous(), mode="shards", **kw)
     ids2, _ = shards.search(queries)

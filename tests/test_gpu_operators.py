@@ -234,6 +234,33 @@ def test_symmetrize_adds_reverse_edges_and_keeps_rows_well_formed(built_lib):
     assert gained > 0
 
 
+def test_symmetrize_cut_inside_the_forward_tail_keeps_the_closest(built_lib):
+    """Rows whose reverse neighbours repeat forward ones leave room for part of the forward tail:
+    the columns kept from it must be its closest ones (a NumPy model of the three priority classes)."""
+    from vectorlink_gpu.kernels import reverse_edges, symmetrize
+    rng = np.random.default_rng(10)
+    nn, d, keep = 600, 12, 6
+    v = unit(rng, nn, 8)                       # low dimension: neighbour relations are mostly mutual
+    kn = oracle.bruteforce_knn(v, v, d, exclude_self=True)
+    dd = oracle.calculate_distances(v, kn)
+    ids, dist = symmetrize(t(v), t(kn), t(dd), keep=keep)
+    ids = n(ids)
+    rev = n(reverse_edges(t(kn), scan=d, keep=keep))
+    into_tail = 0
+    for x in range(nn):
+        want = []
+        for y in list(kn[x, : d - keep]) + [r for r in rev[x] if r != x] + list(kn[x, d - keep:]):
+            if y != MAXINT and y not in want:
+                want.append(y)
+        tail_kept = [y for y in want[:d] if y in kn[x, d - keep:] and y not in rev[x]]
+        into_tail += 0 < len(tail_kept) < keep
+        # the kept part of the tail is a prefix of it (its closest entries)
+        tail = [y for y in kn[x, d - keep:] if y not in rev[x]]
+        assert tail_kept == tail[:len(tail_kept)]
+        assert sorted(want[:d]) == sorted(y for y in ids[x] if y != MAXINT)
+    assert into_tail > 0
+
+
 def test_full_prune_scan_vs_numpy(built_lib):
     """prune_(full=True): every neighbour of y is a detour witness; rows in rising slot order see
     their own punches, other rows are read as they came in."""

@@ -69,6 +69,20 @@ def test_build_vs_reference_host_code(which, mode, c1, small, built_lib):
     assert generate_ann.last_loops == 1
 
 
+@pytest.mark.parametrize("mode", ["fused", "stepwise"])
+def test_multi_round_build_vs_patched_reference(mode, multi, built_lib):
+    """Three rounds of the reference's host code (repaired at the two accidental spots the fixture's
+    generator names): rounds that start from pruned lists with MAXINT tails and carried distances."""
+    from vectorlink_gpu.ann import generate_ann
+    cfg, _ = cfg_of(multi)
+    cfg = dict(cfg)
+    if mode == "stepwise":
+        cfg["stepwise"] = True
+    beams, dist = generate_ann(t(multi["vectors"]), cfg)
+    assert generate_ann.last_loops == int(multi["loops"]) == 3
+    assert np.array_equal(n(beams), multi["beams"]) and np.array_equal(n(dist), multi["distances"])
+
+
 def test_ann_constructor_is_a_drop_in(c1, built_lib):
     from vectorlink_gpu import ANN
     _, kw = cfg_of(c1)

@@ -111,6 +111,18 @@ def test_search_matches_reference_host_code(which, c1, small):
     assert np.array_equal(one.indices, g["search1_ids"])    # un-patched single-query reference call
 
 
+def test_multi_round_build_matches_patched_reference(multi):
+    """Rounds two and three (pruned rows with MAXINT tails, carried distances, the round after a
+    self-recall below 1.0) against the reference's host code, repaired only where it is
+    accidental: the name the prune result is bound to (ann.py:172) and the stability of the last
+    sort of punchout_duplicates_/prune_ (kernels.py:402,466)."""
+    cfg, _ = cfg_of(multi)
+    beams, dist, loops, found = oracle.generate_ann(multi["vectors"], cfg)
+    assert loops == int(multi["loops"]) == 3
+    assert np.array_equal(beams, multi["beams"]) and np.array_equal(dist, multi["distances"])
+    assert found == int(multi["self_recall_found"])
+
+
 def test_recall_of_the_reference_graph(c1):
     cfg, _ = cfg_of(c1)
     sq = oracle.search(c1["vectors"], c1["beams"], c1["queries"], cfg)

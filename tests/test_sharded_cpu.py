@@ -86,3 +86,67 @@ def test_partition_covers_every_row_once():
             assert all(b[i][1] == b[i + 1][0] for i in range(world - 1))
             sizes = [h - l for l, h in b]
             assert max(sizes) - min(sizes) <= 1
+
+
+def _rows_worker(rank, world, port, total, batch, out_dir):
+    """generate_ann's row-split rounds on CPU ranks: the device operators are replaced by
+    oracle-backed stand-ins, everything else (row ranges, whole-batch handling of a batch that
+    straddles two ranks, padded all-gathers, pruning of the own rows only) is the product's code."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from vectorlink_gpu import _lib, ann
+
+    class HostQueue:
+        def __init__(self, num_queues, queue_length, capacity, device=None):
+            self.q = oracle.Queue(num_queues, queue_length, capacity)
+            self.length = queue_length
+
+        indices = property(lambda self: torch.from_numpy(self.q.indices))
+        distances = property(lambda self: torch.from_numpy(self.q.distances))
+
+        def insert(self, ids, dd, exclude=None, output_update=False):
+            return self.q.insert(ids.numpy(), dd.numpy(), None if exclude is None else exclude.numpy(), output_update)
+
+    def stepwise(query_vecs, queue, vectors, beams, config, exclude=None):
+        return oracle.closest_vectors(query_vecs.numpy(), queue.q, vectors.numpy(), beams.contiguous().numpy(), config,
+                                      None if exclude is None else exclude.numpy())
+
+    def prune(beams, distances, full=False, rows=None, out=None):
+        pb, pd = oracle.prune_(beams.numpy(), distances.numpy())
+        if out is None:
+            return torch.from_numpy(pb), torch.from_numpy(pd)
+        lo, hi = rows
+        out[0][lo:hi] = torch.from_numpy(pb[lo:hi])
+        out[1][lo:hi] = torch.from_numpy(pd[lo:hi])
+        return out
+
+    def recall(vectors, beams, config, sample=None):
+        found = oracle.self_recall(vectors.numpy(), beams.numpy(), config, sample.size(0))
+        return found, found / sample.size(0)
+
+    _lib.require_cuda = lambda *a: None
+    ann.Queue = HostQueue
+    ann.closest_vectors_stepwise = stepwise
+    ann.prune_ = prune
+    ann.ann_calculate_recall = recall
+    ann.calculate_distances = lambda v, b, metric="cosine": torch.from_numpy(oracle.calculate_distances(v.numpy(), b.numpy()))
+    ann.excluding_self = lambda start, end, ql, device="cpu": torch.arange(start, end, dtype=torch.int32).unsqueeze(1)
+    ann.primes = lambda size, device="cpu": torch.from_numpy(oracle.primes_table()[:size].copy())
+
+    g = torch.Generator().manual_seed(3)
+    vectors = torch.nn.functional.normalize(torch.randn(total, 12, generator=g), dim=1).contiguous()
+    cfg = oracle.make_config(beam_size=5, batch_size=batch, optimization_loops=2)
+    beams, dd = ann.generate_ann(vectors, dict(cfg, stepwise=True), group=dist.group.WORLD)
+    want_b, want_d, loops, _ = oracle.generate_ann(vectors.numpy(), cfg)
+    assert ann.generate_ann.last_loops == loops
+    assert np.array_equal(beams.numpy(), want_b) and np.array_equal(dd.numpy(), want_d)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,total,batch", [(2, 131, 30), (3, 100, 7), (2, 90, 1000)])
+def test_row_split_build_rounds_equal_the_single_process_build(tmp_path, world, total, batch):
+    """Uneven row ranges, batches that straddle two ranks, a batch larger than the set."""
+    mp.spawn(_rows_worker, args=(world, _free_port(), total, batch, str(tmp_path)), nprocs=world, join=True)

@@ -316,7 +316,7 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
 #define VL_PHASE(i) do { if (timing) { long long t_now = clock64(); tk[i] += t_now - t_prev; t_prev = t_now; } } while (0)
         const int32_t self_id = p.self_base >= 0 ? (int32_t)(p.self_base + row) : VL_MAXINT;
         const int32_t* excl = p.exclude_w > 0 ? p.exclude + row * (int64_t)p.exclude_w : nullptr;
-        const int64_t group = p.group_rows > 0 ? row / p.group_rows : 0;
+        const int64_t group = p.group_rows > 0 ? (p.group_row0 + row) / p.group_rows : 0;
         bool dumped = false;
 
 #pragma unroll 1
@@ -712,7 +712,7 @@ int beam_dispatch(const vl_beam_params* pp, BeamPlan& plan, bool launch, cudaStr
     VL_CHECK_ARG(!p.dump_last || p.out_cols >= p.sq_len + p.pvc * p.graph_w, "vl_beam_search: dump_last needs out_cols >= length + candidates");
     VL_CHECK_ARG(!p.dump_last || p.n_iters <= (p.seen_cap + p.pvc - 1) / p.pvc + 1, "vl_beam_search: dump_last past the last productive iteration");
     VL_CHECK_ARG(p.exclude_w == 0 || p.exclude, "vl_beam_search: exclusion width without a list");
-    VL_CHECK_ARG(p.n_checks >= 0 && p.group_rows >= 0, "vl_beam_search: bad flag shape");
+    VL_CHECK_ARG(p.n_checks >= 0 && p.group_rows >= 0 && p.group_row0 >= 0, "vl_beam_search: bad flag shape");
     VL_CHECK_ARG(p.pvc * (int64_t)p.graph_w <= 65535, "vl_beam_search: %d candidates per iteration exceed 65535", p.pvc * p.graph_w);
     VL_CHECK_ARG(!p.memo || (p.memo_entries >= 2 && (p.memo_entries & (p.memo_entries - 1)) == 0 && (uintptr_t)p.memo % 16 == 0),
                  "vl_beam_search: memo_entries must be a power of two >= 2 and the memo 16-byte aligned");

@@ -376,6 +376,7 @@ static inline VlShape vl_pick_shape(int dim)
 
 // host-side error plumbing shared by the extern "C" entry points
 void vl_set_error(const char* fmt, ...);
+int vl_sm_count();   // SMs of the current device
 #define VL_CHECK_ARG(cond, ...)          \
     do {                                 \
         if (!(cond)) {                   \

@@ -81,7 +81,7 @@ __global__ void flatten_kernel(int32_t* parent, int64_t n)
 unsigned grid_for(int64_t items, int threads)
 {
     int64_t blocks = (items + threads - 1) / threads;
-    const int64_t cap = 148 * 16;                              // 16 CTAs of 256 threads fill an SM
+    const int64_t cap = (int64_t)vl_sm_count() * 16;           // 16 CTAs of 256 threads fill an SM
     if (blocks > cap) blocks = cap;
     return (unsigned)(blocks < 1 ? 1 : blocks);
 }

@@ -82,7 +82,8 @@ int launch_gather(const float* vectors, int64_t n, int dim, const float* queries
     const int64_t total = rows * segs;
     if (total == 0 || seg_len == 0) return 0;
     int64_t blocks = (total + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    if (blocks > 148 * 64) blocks = 148 * 64;  // grid-stride beyond that
+    const int64_t cap = (int64_t)vl_sm_count() * 64;  // grid-stride beyond that
+    if (blocks > cap) blocks = cap;
     const bool aligned = (dim % 4 == 0) && (((uintptr_t)vectors | (uintptr_t)queries) % 16 == 0);
     VlShape shape = vl_pick_shape(dim);
     VL_DISPATCH_SHAPE(shape, {

@@ -33,7 +33,7 @@ __device__ __forceinline__ void warp_bitonic_sort(vl_key_t* keys, int p, int lan
 }
 
 __global__ void __launch_bounds__(kPruneWarps * 32)
-prune_kernel(const int32_t* __restrict__ beams, const float* __restrict__ dist, int64_t n, int w,
+prune_kernel(const int32_t* __restrict__ beams, const float* __restrict__ dist, int64_t n, int64_t x0, int64_t x1, int w,
              int do_punch, int32_t* __restrict__ beams_out, float* __restrict__ dist_out, int out_cols, int p,
              int* __restrict__ status)
 {
@@ -47,7 +47,7 @@ prune_kernel(const int32_t* __restrict__ beams, const float* __restrict__ dist, 
     int32_t* zs = reinterpret_cast<int32_t*>(d + w);
     float* dyz = reinterpret_cast<float*>(zs + w);
 
-    for (int64_t x = (int64_t)blockIdx.x * kPruneWarps + warp; x < n; x += (int64_t)gridDim.x * kPruneWarps) {
+    for (int64_t x = x0 + (int64_t)blockIdx.x * kPruneWarps + warp; x < x1; x += (int64_t)gridDim.x * kPruneWarps) {
         for (int s = lane; s < w; s += 32) {
             int32_t y = beams[x * w + s];
             float dxy = dist[x * w + s];
@@ -119,14 +119,16 @@ prune_kernel(const int32_t* __restrict__ beams, const float* __restrict__ dist, 
 
 }  // namespace
 
-extern "C" int vl_prune(const int32_t* beams, const float* dist, int64_t n, int w, int do_punch,
-                        int32_t* beams_out, float* dist_out, int out_cols, int* status, void* stream)
+extern "C" int vl_prune_rows(const int32_t* beams, const float* dist, int64_t n, int w, int64_t row_lo, int64_t row_hi,
+                             int do_punch, int32_t* beams_out, float* dist_out, int out_cols, int* status, void* stream)
 {
     VL_CHECK_ARG(beams && dist && beams_out && dist_out && status, "vl_prune: null pointer");
     VL_CHECK_ARG(w > 0 && w <= 2048, "vl_prune: row width %d outside 1..2048", w);
     VL_CHECK_ARG(out_cols > 0 && out_cols <= w, "vl_prune: cannot keep %d of %d columns", out_cols, w);
     VL_CHECK_ARG(beams != beams_out && dist != dist_out, "vl_prune: output must not alias input");
-    if (n == 0) return 0;
+    VL_CHECK_ARG(0 <= row_lo && row_lo <= row_hi && row_hi <= n, "vl_prune: rows [%lld, %lld) outside [0, %lld)",
+                 (long long)row_lo, (long long)row_hi, (long long)n);
+    if (row_hi == row_lo) return 0;
     int p = 2;
     while (p < w) p <<= 1;
     size_t per_warp = (size_t)p + 2 * (size_t)((w + 1) / 2) * 2;
@@ -135,10 +137,18 @@ extern "C" int vl_prune(const int32_t* beams, const float* dist, int64_t n, int 
         cudaError_t e = cudaFuncSetAttribute(prune_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         VL_CHECK_ARG(e == cudaSuccess, "vl_prune: %s", cudaGetErrorString(e));
     }
-    int64_t blocks = (n + kPruneWarps - 1) / kPruneWarps;
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    prune_kernel<<<(unsigned)blocks, kPruneWarps * 32, smem, (cudaStream_t)stream>>>(beams, dist, n, w, do_punch, beams_out,
-                                                                                   dist_out, out_cols, p, status);
+    int64_t blocks = (row_hi - row_lo + kPruneWarps - 1) / kPruneWarps;
+    const int64_t cap = (int64_t)vl_sm_count() * 32;
+    if (blocks > cap) blocks = cap;
+    prune_kernel<<<(unsigned)blocks, kPruneWarps * 32, smem, (cudaStream_t)stream>>>(beams, dist, n, row_lo, row_hi, w, do_punch,
+                                                                                   beams_out, dist_out, out_cols, p, status);
     VL_CHECK_LAUNCH("prune_kernel");
     return 0;
+}
+
+extern "C" int vl_prune(const int32_t* beams, const float* dist, int64_t n, int w, int do_punch,
+                        int32_t* beams_out, float* dist_out, int out_cols, int* status, void* stream)
+{
+    VL_CHECK_ARG(n >= 0, "vl_prune: negative row count");
+    return vl_prune_rows(beams, dist, n, w, 0, n, do_punch, beams_out, dist_out, out_cols, status, stream);
 }

@@ -324,12 +324,14 @@ extern "C" int vl_seen_add(int32_t* seen, int64_t b, int e, const int32_t* visit
     VL_CHECK_ARG(seen && visit && scratch && first_out, "vl_seen_add: null pointer");
     VL_CHECK_ARG(e >= 0 && e <= kMaxSortWidth, "vl_seen_add: width %d outside 0..%d", e, kMaxSortWidth);
     cudaStream_t st = (cudaStream_t)stream;
-    if (e == 0 || b == 0) {  // utils.py:67-69: no column at all -> None
-        int minus = -1;
-        cudaMemcpyAsync(first_out, &minus, sizeof(int), cudaMemcpyHostToDevice, st);
+    cudaError_t ce;
+    if (e == 0 || b == 0) {  // utils.py:67-69: no column at all -> None; -1 is four 0xFF bytes
+        ce = cudaMemsetAsync(first_out, 0xFF, sizeof(int), st);
+        VL_CHECK_ARG(ce == cudaSuccess, "vl_seen_add: cudaMemsetAsync: %s", cudaGetErrorString(ce));
         return 0;
     }
-    cudaMemsetAsync(scratch, 0, sizeof(int) * e, st);
+    ce = cudaMemsetAsync(scratch, 0, sizeof(int) * e, st);
+    VL_CHECK_ARG(ce == cudaSuccess, "vl_seen_add: cudaMemsetAsync: %s", cudaGetErrorString(ce));
     column_used_kernel<<<blocks_for(b * e, 256), 256, 0, st>>>(seen, b * e, e, scratch);
     VL_CHECK_LAUNCH("column_used_kernel");
     first_free_column_kernel<<<1, 256, 0, st>>>(scratch, e, first_out);
@@ -362,6 +364,8 @@ extern "C" int vl_seen_add(int32_t* seen, int64_t b, int e, const int32_t* visit
 
 // VL_SEEN_NOALLOC_MAX_WIDTH (vlgpu.h): most columns (`e`) the fixed scratch can serve
 static __device__ __align__(256) int g_seen_scratch[VL_SEEN_NOALLOC_MAX_WIDTH];
+// the kernels that consume the flags are sized for rows of at most kMaxSortWidth columns
+static_assert(VL_SEEN_NOALLOC_MAX_WIDTH <= kMaxSortWidth, "the fixed scratch must not be wider than a sortable row");
 
 namespace {
 
@@ -397,9 +401,9 @@ extern "C" int vl_seen_add_noalloc(int32_t* seen, int64_t b, int e, const int32_
                  "vl_seen_add_noalloc: list width %d exceeds the fixed scratch of %d columns; use vl_seen_add with a "
                  "caller-provided scratch buffer", e, VL_SEEN_NOALLOC_MAX_WIDTH);
     cudaStream_t st = (cudaStream_t)stream;
-    if (e == 0 || b == 0) {
-        int minus = -1;
-        cudaMemcpyAsync(first_out, &minus, sizeof(int), cudaMemcpyHostToDevice, st);
+    if (e == 0 || b == 0) {   // -1 is four 0xFF bytes: no host buffer involved
+        cudaError_t ze = cudaMemsetAsync(first_out, 0xFF, sizeof(int), st);
+        VL_CHECK_ARG(ze == cudaSuccess, "vl_seen_add_noalloc: cudaMemsetAsync: %s", cudaGetErrorString(ze));
         return 0;
     }
     int* scratch = nullptr;

@@ -22,7 +22,7 @@ c_intp = ctypes.POINTER(ctypes.c_int)
 EXPORTS = [
     "vl_last_error", "vl_abi_version", "vl_calculate_distances", "vl_search_from_seeds", "vl_queue_insert",
     "vl_queue_pop", "vl_punchout_excluded", "vl_dedup_adjacent", "vl_sort_pairs", "vl_dedup_sort_ids",
-    "vl_seen_add", "vl_seen_add_noalloc", "vl_prune", "vl_reverse_edges", "vl_connected_components", "vl_beam_search",
+    "vl_seen_add", "vl_seen_add_noalloc", "vl_prune", "vl_prune_rows", "vl_reverse_edges", "vl_connected_components", "vl_beam_search",
     "vl_beam_search_plan",
 ]
 
@@ -44,6 +44,7 @@ class BeamParams(ctypes.Structure):
         ("group_full", ctypes.c_void_p), ("status", ctypes.c_void_p),
         ("memo", ctypes.c_void_p), ("memo_slots", ctypes.c_int64), ("stats", ctypes.c_void_p),
         ("flags", ctypes.c_int32), ("reserved", ctypes.c_int32), ("row_ticket", ctypes.c_void_p),
+        ("group_row0", ctypes.c_int64),
     ]
 
 
@@ -78,6 +79,7 @@ def lib() -> ctypes.CDLL:
         _lib.vl_seen_add.argtypes = [P, L, I, P, I, P, P, P]
         _lib.vl_seen_add_noalloc.argtypes = [P, L, I, P, I, P, P]
         _lib.vl_prune.argtypes = [P, P, L, I, I, P, P, I, P, P]
+        _lib.vl_prune_rows.argtypes = [P, P, L, I, L, L, I, P, P, I, P, P]
         _lib.vl_reverse_edges.argtypes = [P, L, I, I, I, P, P, P, P, I, P, P, P]
         _lib.vl_connected_components.argtypes = [P, P, L, I, L, ctypes.c_float, P, P, P]
         _lib.vl_beam_search.argtypes = [ctypes.POINTER(BeamParams), P]

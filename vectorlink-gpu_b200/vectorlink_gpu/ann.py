@@ -20,7 +20,7 @@ from . import _lib
 from ._lib import BeamParams, check, lib, ptr, stream_of
 from .constants import MAXFLOAT, MAXINT, PRIMES_HOST
 from .kernels import calculate_distances, connected_components, metric_code, prune_, search_from_seeds, sort_pairs_
-from .log import log_time
+from .log import log_time, nvtx_range
 from . import log as _log
 from .queue import Queue
 from .utils import add_new_to_seen_, generate_circulant_beams, generate_queue_circulants, primes
@@ -29,6 +29,7 @@ FUSED_MAX_SMEM_PER_ROW = 200 * 1024
 # When set to a list, every fused-kernel launch appends its CUDA events (recorded on the
 # launching stream) and its count of distance evaluations: the benchmark's roofline figures.
 PROFILE = None
+PROFILE_TAG = "search"     # which phase the launches being profiled belong to (generate_ann sets it per round)
 # When set to an int64 CUDA tensor of 16 zeros, the fused kernel adds its work counters and
 # per-phase warp cycles to it (layout: `stats` in include/vlgpu.h).
 STATS = None
@@ -68,10 +69,13 @@ def loop_bounds(config: Dict) -> Tuple[int, int, int]:
 
 
 def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
-                 config, n_iters, dump_last, exclude, self_base, group_rows, flags, full, stats=None):
+                 config, n_iters, dump_last, exclude, self_base, group_rows, flags, full, stats=None, group_row0=0):
     pvc = config["parallel_visit_count"]
     if stats is None:
         stats = STATS
+    if stats is None and PROFILE is not None:
+        # a profiled launch reports its own counters (gathered candidates, rows, iterations)
+        stats = torch.zeros(24, dtype=torch.int64, device=vectors.device)
     vq_len = config["visit_queue_factor"] * config["beam_size"]
     p = BeamParams()
     p.vectors = vectors.data_ptr()
@@ -101,6 +105,7 @@ def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len
     p.exclude = exclude.data_ptr() if exclude is not None else 0
     p.self_base = self_base
     p.group_rows = group_rows
+    p.group_row0 = group_row0
     p.changed_flags = flags.data_ptr()
     p.n_checks = flags.size(1)
     p.group_full = full.data_ptr()
@@ -137,7 +142,8 @@ def _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len
         end.record()
         k_none = (p.seen_cap + pvc - 1) // pvc + 1
         PROFILE.append({"start": start, "end": end, "rows": int(p.rows), "graph_w": int(p.graph_w),
-                        "iterations": int(min(n_iters, k_none)), "evals": int(p.rows) * min(n_iters, k_none) * pvc * int(p.graph_w)})
+                        "iterations": int(min(n_iters, k_none)), "evals": int(p.rows) * min(n_iters, k_none) * pvc * int(p.graph_w),
+                        "memo": bool(p.memo), "stats": stats if stats is not STATS else None, "tag": PROFILE_TAG})
 
 
 _memo_cache = {}
@@ -164,30 +170,49 @@ def _natural_end(flag_row: List[int], config: Dict) -> int:
 
 
 def _fused_batches(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, sq_cap, config, exclude,
-                   self_base, group_rows, out_ids, out_dist, out_cols, stepwise):
+                   self_base, group_rows, out_ids, out_dist, out_cols, stepwise, group_row0=0, total_groups=None,
+                   reduce_group=None):
     """Runs the fused search over `queries` split in batches of `group_rows` (the reference's
     host loop, ann.py:132-166) in one launch, then repairs the batches for which the
     reference's batch-wide decisions differ from the budgeted schedule: a batch whose heads
     stopped changing at an earlier check is re-run up to that iteration, a batch in which
-    every row popped a MAXINT at some point goes through `stepwise`.  Returns the iteration
-    count of every batch."""
+    every row popped a MAXINT at some point goes through `stepwise(lo, hi)` (rows of this
+    launch).  Returns the iteration count of every batch this launch touched.
+
+    `group_row0`: position of query row 0 in the host loop (a launch may start inside a batch);
+    `total_groups`: batches of the whole loop; `reduce_group`: a torch.distributed group whose
+    ranks each run a slice of the same loop - the two batch-wide flags are then OR-ed across the
+    ranks (one small all-reduce) before any decision is taken, because a batch can straddle ranks."""
     rows = queries.size(0)
     k_none, n_checks, n_max = loop_bounds(config)
-    groups = (rows + group_rows - 1) // group_rows if rows else 0
+    if total_groups is None:
+        total_groups = (group_row0 + rows + group_rows - 1) // group_rows if rows else 0
     dev = vectors.device
-    flags = torch.zeros((max(groups, 1), max(n_checks, 1)), dtype=torch.int32, device=dev)
-    full = torch.zeros((max(groups, 1),), dtype=torch.int32, device=dev)
-    if rows == 0:
+    nc = max(n_checks, 1)
+    ng = max(total_groups, 1)
+    # one buffer for both flag arrays: one all-reduce, one read-back
+    flag_buf = torch.zeros(ng * nc + ng, dtype=torch.int32, device=dev)
+    flags = flag_buf[: ng * nc].view(ng, nc)
+    full = flag_buf[ng * nc:]
+    if rows == 0 and reduce_group is None:
         return []
     # a caller that wants to know how useful the distance memo is on this graph (generate_ann's
     # self-recall check) gets the share of candidates that had to be gathered
     counters = None
     if config.get("measure_gathered") and config.get("memo", True):
         counters = torch.zeros(24, dtype=torch.int64, device=dev)
-    _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
-                 config, n_max, False, exclude, self_base, group_rows, flags, full, counters)
-    flags_h = flags.cpu().tolist()
-    full_h = full.cpu().tolist()
+    if rows:
+        _launch_beam(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_len, out_ids, out_dist, out_cols,
+                     config, n_max, False, exclude, self_base, group_rows, flags, full, counters, group_row0)
+    if reduce_group is not None:
+        import torch.distributed as dist
+        with nvtx_range("vl.flags_allreduce"):
+            dist.all_reduce(flag_buf, op=dist.ReduceOp.MAX, group=reduce_group)
+    if rows == 0:
+        return []
+    host = flag_buf.cpu()
+    flags_h = host[: ng * nc].view(ng, nc).tolist()
+    full_h = host[ng * nc:].tolist()
     if counters is not None:
         if STATS is not None:
             shared = min(STATS.numel(), counters.numel())
@@ -196,8 +221,8 @@ def _fused_batches(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_l
         offered = c[7] * config["parallel_visit_count"] * graph.size(1)
         _fused_batches.last_gathered = c[1] / offered if offered else None
     counts = []
-    for gi in range(groups):
-        lo, hi = gi * group_rows, min(rows, (gi + 1) * group_rows)
+    for gi in range(group_row0 // group_rows, (group_row0 + rows - 1) // group_rows + 1):
+        lo, hi = max(0, gi * group_rows - group_row0), min(rows, (gi + 1) * group_rows - group_row0)
         end = _natural_end(flags_h[gi][:n_checks], config) if n_checks else n_max
         if not full_h[gi]:
             counts.append(stepwise(lo, hi))
@@ -209,7 +234,7 @@ def _fused_batches(vectors, graph, queries, seed_ids, seed_dist, seed_cols, sq_l
         # is a whole-row sort so that the columns behind `length` match too
         tmp_i = torch.empty((hi - lo, sq_cap), dtype=torch.int32, device=dev)
         tmp_d = torch.empty((hi - lo, sq_cap), dtype=torch.float32, device=dev)
-        f2 = torch.zeros((1, max(n_checks, 1)), dtype=torch.int32, device=dev)
+        f2 = torch.zeros((1, nc), dtype=torch.int32, device=dev)
         u2 = torch.zeros((1,), dtype=torch.int32, device=dev)
         _launch_beam(vectors, graph, queries[lo:hi], seed_ids[lo:hi], seed_dist[lo:hi], seed_cols, sq_len, tmp_i, tmp_d,
                      sq_cap, config, end, True, exclude[lo:hi] if exclude is not None else None,
@@ -313,12 +338,17 @@ def excluding_self(start, end, queue_length, device="cuda"):
     return torch.arange(start, end, dtype=torch.int32, device=device).unsqueeze(1).contiguous()
 
 
-def _share_rows(t: Tensor, bounds, group) -> None:
-    """Every rank ends up with every row block of `t`: block s is broadcast by its owner."""
+def _gather_row_blocks(buf: Tensor, per: int, group) -> None:
+    """`buf` [world * per, ...] holds rank r's rows in block r; afterwards every rank holds every
+    block (one in-place all-gather)."""
     import torch.distributed as dist
-    for s, (lo, hi) in enumerate(bounds):
-        if hi > lo:
-            dist.broadcast(t[lo:hi], src=dist.get_global_rank(group, s) if group is not None else s, group=group)
+    rank = dist.get_rank(group)
+    mine = buf[rank * per:(rank + 1) * per]
+    if buf.is_cuda:
+        dist.all_gather_into_tensor(buf.view(-1), mine.reshape(-1), group=group)
+    else:
+        world = dist.get_world_size(group)
+        dist.all_gather([buf[r * per:(r + 1) * per] for r in range(world)], mine.clone(), group=group)
 
 
 def generate_ann(vectors: Tensor, config: Dict, group=None) -> Tuple[Tensor, Tensor]:
@@ -332,77 +362,116 @@ def generate_ann(vectors: Tensor, config: Dict, group=None) -> Tuple[Tensor, Ten
     MAXINT neighbour yields sentinels instead of an out-of-range read.
 
     With `group` (a torch.distributed group whose ranks all hold the same `vectors`) the rows of
-    each round are split across the ranks in whole batches and the new neighbour lists are
-    exchanged after the search, so every rank ends with the same graph as a single-GPU build."""
+    each round are split evenly across the ranks (a batch of the host loop may straddle two
+    ranks: its batch-wide flags are OR-ed across them), each rank searches and prunes its own
+    rows, and the new lists are all-gathered, so every rank ends with the same graph as a
+    single-GPU build.
+
+    config["init"] == "knn_tile" (added; default "circulant" = the reference) starts from the
+    lists of the tensor-core tile pass instead of the circulant graph (see knn_tile.py)."""
     _lib.require_cuda(vectors)
     (num_vecs, vec_dim) = vectors.size()
     beam_size = config["beam_size"]
     queue_length = beam_size * config["beam_queue_factor"]
     dev = vectors.device
     metric = _metric_of(config)
-    neighbor_primes = primes(queue_length, dev)
-    beams = generate_circulant_beams(num_vecs, neighbor_primes)
-    assert beams.dtype == torch.int32
-    beam_distances = calculate_distances(vectors, beams, metric=metric)
     remaining_capacity = queue_length * config["parallel_visit_count"]
     capacity = queue_length + remaining_capacity
     batch_size = config["batch_size"]
     fused = not config.get("stepwise", False) and _fused_shape_ok(vectors, queue_length, queue_length, capacity, config)
-    row_lo, row_hi, bounds = 0, num_vecs, None
+    world, rank = 1, 0
     if group is not None:
         import torch.distributed as dist
         world, rank = dist.get_world_size(group), dist.get_rank(group)
-        if world > 1:
-            n_batches = (num_vecs + batch_size - 1) // batch_size
-            from .sharded import partition_rows
-            bounds = [(min(num_vecs, lo * batch_size), min(num_vecs, hi * batch_size))
-                      for lo, hi in partition_rows(n_batches, world)]
-            row_lo, row_hi = bounds[rank]
+    per = (num_vecs + world - 1) // world              # rows per rank; the last ranks may hold fewer
+    row_lo, row_hi = min(num_vecs, rank * per), min(num_vecs, (rank + 1) * per)
+    n_batches = (num_vecs + batch_size - 1) // batch_size
+
+    with nvtx_range("vl.start_graph"):
+        if config.get("init", "circulant") == "knn_tile":
+            from .knn_tile import knn_start_graph
+            (beams, beam_distances) = knn_start_graph(vectors, queue_length, config, group=group)
+        else:
+            neighbor_primes = primes(queue_length, dev)
+            beams = generate_circulant_beams(num_vecs, neighbor_primes)
+            assert beams.dtype == torch.int32
+            beam_distances = calculate_distances(vectors, beams, metric=metric)
+
     loops_run = 0
     memo_useful = True
     for i in range(0, config["optimization_loops"]):
         print_timestamp(f"start of cagra loop {i}")
-        next_beams = torch.empty_like(beams)
-        next_beam_distances = torch.empty_like(beam_distances)
+        # padded to world * per rows so that the exchange is one equal-sized all-gather
+        next_pad = torch.empty((world * per, queue_length), dtype=torch.int32, device=dev)
+        next_dist_pad = torch.empty((world * per, queue_length), dtype=torch.float32, device=dev)
+        next_beams = next_pad[:num_vecs]
+        next_beam_distances = next_dist_pad[:num_vecs]
 
-        def batch_stepwise(lo, hi):
-            lo, hi = lo + row_lo, hi + row_lo
-            exclude = excluding_self(lo, hi, queue_length, dev)
-            queue = Queue(hi - lo, queue_length, capacity, device=dev)
-            queue.insert(beams.narrow(0, lo, hi - lo), beam_distances.narrow(0, lo, hi - lo))
-            n = closest_vectors_stepwise(vectors[lo:hi], queue, vectors, beams, config, exclude)
-            next_beams.narrow(0, lo, hi - lo).copy_(queue.indices.narrow(1, 0, queue_length))
-            next_beam_distances.narrow(0, lo, hi - lo).copy_(queue.distances.narrow(1, 0, queue_length))
+        def whole_batch_stepwise(glo, ghi):
+            """One batch of the reference's host loop (global rows), operator by operator."""
+            exclude = excluding_self(glo, ghi, queue_length, dev)
+            queue = Queue(ghi - glo, queue_length, capacity, device=dev)
+            queue.insert(beams.narrow(0, glo, ghi - glo), beam_distances.narrow(0, glo, ghi - glo))
+            n = closest_vectors_stepwise(vectors[glo:ghi], queue, vectors, beams, config, exclude)
+            next_beams.narrow(0, glo, ghi - glo).copy_(queue.indices.narrow(1, 0, queue_length))
+            next_beam_distances.narrow(0, glo, ghi - glo).copy_(queue.distances.narrow(1, 0, queue_length))
             return n
 
+        def batch_stepwise(lo, hi):
+            # rows [lo, hi) of this rank's launch lie in one batch; the operator path couples the rows of
+            # a batch, so the whole batch is run (a rank that holds the rest of it computes the same rows)
+            g = (row_lo + lo) // batch_size
+            return whole_batch_stepwise(g * batch_size, min(num_vecs, (g + 1) * batch_size))
+
         round_config = config
-        if (i == 0 or not memo_useful) and "memo" not in config and "memo_entries" not in config:
+        circulant_round = i == 0 and config.get("init", "circulant") == "circulant"
+        if (circulant_round or not memo_useful) and "memo" not in config and "memo_entries" not in config:
             # the circulant start graph makes candidates that hardly ever repeat within a row
             # (6 % memo hits measured): the first round runs faster without the memo; so do later
             # rounds on data where the last self-recall check gathered nearly every candidate
             round_config = dict(config, memo=False)
-        if row_hi > row_lo:
+        global PROFILE_TAG
+        with nvtx_range(f"vl.round{i}.search"):
+            PROFILE_TAG = f"round{i}"
             if fused:
                 _fused_batches(vectors, beams, vectors[row_lo:row_hi], beams[row_lo:row_hi],
                                beam_distances[row_lo:row_hi], queue_length, queue_length, capacity, round_config, None,
                                row_lo, batch_size, next_beams[row_lo:row_hi], next_beam_distances[row_lo:row_hi],
-                               queue_length, batch_stepwise)
-            else:
-                for lo in range(0, row_hi - row_lo, batch_size):
-                    batch_stepwise(lo, min(row_hi - row_lo, lo + batch_size))
-        if bounds is not None:
-            _share_rows(next_beams, bounds, group)
-            _share_rows(next_beam_distances, bounds, group)
+                               queue_length, batch_stepwise, group_row0=row_lo, total_groups=n_batches,
+                               reduce_group=group if world > 1 else None)
+            elif row_hi > row_lo:
+                for g in range(row_lo // batch_size, (row_hi - 1) // batch_size + 1):
+                    whole_batch_stepwise(g * batch_size, min(num_vecs, (g + 1) * batch_size))
+        if world > 1:
+            with nvtx_range(f"vl.round{i}.exchange"):
+                _gather_row_blocks(next_pad, per, group)
+                _gather_row_blocks(next_dist_pad, per, group)
 
-        if config["prune"]:
-            (beams, beam_distances) = prune_(next_beams, next_beam_distances, full=config.get("prune_mode") == "full")
-        else:
-            (beams, beam_distances) = (next_beams, next_beam_distances)
+        with nvtx_range(f"vl.round{i}.prune"):
+            if config["prune"]:
+                full_scan = config.get("prune_mode") == "full"
+                if world > 1:
+                    # a row's detour witnesses are read from the other rows as they came out of the search,
+                    # so each rank prunes its own rows from the gathered lists and the results are gathered
+                    out_pad = torch.empty_like(next_pad)
+                    out_dist_pad = torch.empty_like(next_dist_pad)
+                    prune_(next_beams, next_beam_distances, full=full_scan, rows=(row_lo, row_hi),
+                           out=(out_pad[:num_vecs], out_dist_pad[:num_vecs]))
+                    _gather_row_blocks(out_pad, per, group)
+                    _gather_row_blocks(out_dist_pad, per, group)
+                    (beams, beam_distances) = (out_pad[:num_vecs], out_dist_pad[:num_vecs])
+                else:
+                    (beams, beam_distances) = prune_(next_beams, next_beam_distances, full=full_scan)
+            else:
+                (beams, beam_distances) = (next_beams, next_beam_distances)
         loops_run += 1
         prefix = min(num_vecs, 1000)
         _fused_batches.last_gathered = None
-        (found, recall) = ann_calculate_recall(vectors, beams.narrow_copy(1, 0, beam_size),
-                                               dict(config, measure_gathered=True), sample=vectors[:prefix])
+        with nvtx_range(f"vl.round{i}.recall"):
+            PROFILE_TAG = "self_recall"
+            (found, recall) = ann_calculate_recall(vectors, beams.narrow_copy(1, 0, beam_size),
+                                                   dict(config, measure_gathered=True), sample=vectors[:prefix])
+        PROFILE_TAG = "search"
         if _fused_batches.last_gathered is not None:
             memo_useful = _fused_batches.last_gathered <= MEMO_USELESS_ABOVE
         if recall == 1.0:

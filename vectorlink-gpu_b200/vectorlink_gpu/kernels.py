@@ -120,23 +120,32 @@ def punchout_duplicates_(ids: Tensor, distances: Tensor):
     return (ids, distances)
 
 
-def prune_(beams: Tensor, distances: Tensor, out_cols: Optional[int] = None, punch: bool = True, full: bool = False):
+def prune_(beams: Tensor, distances: Tensor, out_cols: Optional[int] = None, punch: bool = True, full: bool = False,
+           rows: Optional[Tuple[int, int]] = None, out: Optional[Tuple[Tensor, Tensor]] = None):
     """kernels.py:441-468: remove detourable links (x->z when d_xz > d_xy and d_xz > d_yz, z the
     first neighbour of y), then order every row by distance.  Returns new (beams, distances);
     `out_cols` (added) keeps only the first columns; `full` (added) tests every neighbour of y as the
     detour witness, which is what the reference's docstring describes (its launch only ever
-    looks at y's first neighbour)."""
+    looks at y's first neighbour); `rows` = (lo, hi) (added) prunes only those rows - the others
+    are read, their output rows are left untouched - and `out` (added) gives the output tensors."""
     assert beams.dtype == torch.int32
     assert distances.dtype == torch.float32
     assert beams.is_contiguous() and distances.is_contiguous()
     _lib.require_cuda(beams, distances)
     (batch_size, beam_size) = beams.size()
     cols = beam_size if out_cols is None else out_cols
-    out_b = torch.empty((batch_size, cols), dtype=torch.int32, device=beams.device)
-    out_d = torch.empty((batch_size, cols), dtype=torch.float32, device=beams.device)
-    check(lib().vl_prune(ptr(beams), ptr(distances), ctypes.c_int64(batch_size), beam_size, (2 if full else 1) if punch else 0,
-                         ptr(out_b), ptr(out_d), cols, ptr(_lib.status_word(beams.device)), stream_of(beams)),
-          "vl_prune")
+    if out is None:
+        out_b = torch.empty((batch_size, cols), dtype=torch.int32, device=beams.device)
+        out_d = torch.empty((batch_size, cols), dtype=torch.float32, device=beams.device)
+    else:
+        (out_b, out_d) = out
+        assert out_b.dtype == torch.int32 and out_d.dtype == torch.float32
+        assert out_b.is_contiguous() and out_d.is_contiguous()
+        assert tuple(out_b.shape) == (batch_size, cols) and tuple(out_d.shape) == (batch_size, cols)
+    (lo, hi) = (0, batch_size) if rows is None else rows
+    check(lib().vl_prune_rows(ptr(beams), ptr(distances), ctypes.c_int64(batch_size), beam_size, ctypes.c_int64(lo),
+                              ctypes.c_int64(hi), (2 if full else 1) if punch else 0, ptr(out_b), ptr(out_d), cols,
+                              ptr(_lib.status_word(beams.device)), stream_of(beams)), "vl_prune_rows")
     return (out_b, out_d)
 
 
@@ -231,15 +240,14 @@ def symmetrize(vectors: Tensor, beams: Tensor, distances: Tensor, keep: Optional
     rev_dist = calculate_distances(vectors, rev, metric=metric)
     own = torch.arange(n, device=beams.device, dtype=torch.int32).unsqueeze(1)
     rev = torch.where(rev == own, torch.full_like(rev, MAXINT), rev)
-    # priority classes through a distance bias that is removed after the cut: 0 forward head,
-    # 1 reverse, 2 forward tail; duplicates keep their best class because equal ids are punched
-    # after a sort by (class, distance, id)
+    # three priority classes, concatenated in priority order: 0 forward head, 1 reverse, 2 forward
+    # tail.  Within a class the columns keep the order they arrive in (forward lists by distance,
+    # reverse lists by the lister's rank), so "earlier column" means "better" throughout.
     ids = torch.cat([beams[:, : d - keep], rev, beams[:, d - keep:]], 1).contiguous()
     dist = torch.cat([distances[:, : d - keep], rev_dist, distances[:, d - keep:]], 1).contiguous()
-    cls = torch.cat([torch.zeros((n, d - keep)), torch.ones((n, keep)), torch.full((n, keep), 2.0)], 1).to(dist.device)
-    cls = torch.where(ids == MAXINT, torch.full_like(cls, 3.0), cls)
-    order = torch.argsort(cls * 4 + (ids.float() / 2 ** 31), dim=1, stable=True)      # class, then id: first copy wins
-    ids, dist, cls = (torch.gather(t, 1, order) for t in (ids, dist, cls))
+    cls = torch.cat([torch.zeros((n, d - keep), dtype=torch.int32), torch.ones((n, keep), dtype=torch.int32),
+                     torch.full((n, keep), 2, dtype=torch.int32)], 1).to(dist.device)
+    cls = torch.where(ids == MAXINT, torch.full_like(cls, 3), cls)
     # drop repeated ids keeping the first (best class) occurrence
     by_id = torch.argsort(ids, dim=1, stable=True)
     sid = torch.gather(ids, 1, by_id)
@@ -247,7 +255,7 @@ def symmetrize(vectors: Tensor, beams: Tensor, distances: Tensor, keep: Optional
     dup_sorted[:, 1:] = sid[:, 1:] == sid[:, :-1]
     dup = torch.zeros_like(dup_sorted).scatter(1, by_id, dup_sorted)
     ids = torch.where(dup, torch.full_like(ids, MAXINT), ids)
-    cls = torch.where(dup | (ids == MAXINT), torch.full_like(cls, 3.0), cls)
+    cls = torch.where(dup | (ids == MAXINT), torch.full_like(cls, 3), cls)
     keep_order = torch.argsort(cls, dim=1, stable=True)[:, :d]
     ids = torch.gather(ids, 1, keep_order).contiguous()
     dist = torch.gather(dist, 1, keep_order)

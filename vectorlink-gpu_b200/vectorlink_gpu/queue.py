@@ -33,7 +33,9 @@ class Queue:
     def insert(self, vector_id_batch: Tensor, distances_batch: Tensor, exclude: Optional[Tensor] = None,
                output_update: bool = False):
         """queue.py:37-61: candidates into the columns behind `length`, excluded ids punched,
-        whole row re-ordered and de-duplicated; optionally returns head != previous head."""
+        whole row re-ordered and de-duplicated; optionally returns head != previous head.
+        The reference rebinds `.indices`/`.distances` to freshly sorted tensors; here the rows are
+        sorted in place, so a caller that kept the old tensors sees the new contents."""
         (batches, size_per_batch) = vector_id_batch.size()
         (_, capacity) = self.indices.size()
         assert size_per_batch <= capacity - self.length
@@ -56,13 +58,15 @@ class Queue:
         return None
 
     def print(self, tail: Optional[bool] = False):
-        (_bs, dim) = self.size()
-        print(self.indices.narrow(1, 0, self.length))
-        print(self.distances.narrow(1, 0, self.length))
+        """queue.py:78-85: show the heads (ids, then distances); with `tail` also the columns
+        behind `length`."""
+        sections = [("head", 0, self.length)]
         if tail:
-            print("----------------")
-            print(self.indices.narrow(1, self.length, dim - self.length))
-            print(self.distances.narrow(1, self.length, dim - self.length))
+            sections.append(("tail", self.length, self.indices.size(1) - self.length))
+        for label, start, width in sections:
+            print(f"-- {label}: columns {start}..{start + width - 1}")
+            print(self.indices.narrow(1, start, width))
+            print(self.distances.narrow(1, start, width))
 
     def pop_n_ids(self, n: int):
         """queue.py:87-95: the first min(length, n) ids; their slots become sentinels and the
