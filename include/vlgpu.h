@@ -34,6 +34,7 @@ extern "C" {
 #define VL_METRIC_SQL2 1
 #define VL_STATUS_BAD_ID 1
 #define VL_STATUS_OVERFLOW 2
+#define VL_STATUS_TIMEOUT 4   /* a bounded in-kernel wait ran out; the launch's results are not valid */
 
 /* Text of the last rejected call on this host thread. */
 const char* vl_last_error(void);
@@ -134,6 +135,27 @@ int vl_reverse_edges(const int32_t* beams, int64_t n, int d, int scan, int phase
  * labels[x] (int32 [n]) = the smallest node id of x's component. */
 int vl_connected_components(const int32_t* ids, const float* dist, int64_t n, int w, int64_t ld, float threshold,
                             int32_t* labels, int* status, void* stream);
+
+/* Initial-kNN tile pass (not in the reference, which starts every build from the circulant graph
+ * of utils.py:35-41 / ann.py:116-118): tensor-core proposals of near neighbours for an opt-in
+ * start graph.  Two steps.
+ *
+ * vl_knn_prepare: bf16 copy of the rows, zero-padded to dim_pad columns (a multiple of 64), and
+ * |row|^2 in fp32 (sqnorm_out, may be NULL).
+ *
+ * vl_knn_tile: for every row in [row_lo, row_hi) the ids of the VL_KNN_TILE_K candidates with
+ * the smallest approximate score in each of `segments` equal parts of [cand_lo, cand_hi) - bf16
+ * inner products accumulated in fp32 on the tensor cores (tcgen05.mma, operands staged by TMA),
+ * score = sqnorm[c] - 2<q, c> (squared L2) or -2<q, c> when sqnorm == NULL (cosine).  The row
+ * itself is never proposed.  out_ids [row_hi - row_lo, segments * VL_KNN_TILE_K], best first
+ * within a part, MAXINT-padded.  The ids are PROPOSALS: the caller re-evaluates them with
+ * vl_calculate_distances and orders them with vl_sort_pairs, so no bf16 value reaches a graph.
+ * A wait inside the kernel that runs out sets VL_STATUS_TIMEOUT in *status. */
+#define VL_KNN_TILE_K 32
+int vl_knn_prepare(const float* vectors, int64_t n, int dim, uint16_t* bf16_out, int dim_pad, float* sqnorm_out,
+                   void* stream);
+int vl_knn_tile(const uint16_t* rows_bf16, int64_t n, int dim_pad, const float* sqnorm, int64_t row_lo, int64_t row_hi,
+                int64_t cand_lo, int64_t cand_hi, int segments, int32_t* out_ids, int* status, void* stream);
 
 /* closest_vectors (ann.py:37-93) as one kernel: the whole budgeted beam search of every query
  * row, with the search queue, the visit queue and the visited set of a row held on chip by

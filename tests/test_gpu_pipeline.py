@@ -356,3 +356,103 @@ def test_build_with_tiny_batches_follows_the_reference_batch_coupling(batch_size
     gb, gd = generate_ann(t(vectors), dict(cfg))
     assert generate_ann.last_loops == loops
     assert np.array_equal(n(gb), wb) and np.array_equal(n(gd), wd)
+
+
+# ---- the benchmark configurations' own queue shapes, bit for bit against the oracle ----------
+
+def sift_like(rng, count, dim=128, centres=256):
+    """Config-2 recipe: centres uniform in [0,255], point = centre + N(0, 20^2), rounded, clipped."""
+    c = rng.uniform(0, 255, (centres, dim))
+    pts = c[rng.integers(0, centres, count)] + rng.normal(0, 20, (count, dim))
+    return np.round(pts).clip(0, 255).astype(np.float32)
+
+
+def embed_like(rng, count, dim, centres, noise, unit_centres=True):
+    """Config-3/5 recipe: centres N(0,1) (normalised for config 3), point = centre + N(0, noise^2)
+    per dimension, renormalised."""
+    c = rng.standard_normal((centres, dim))
+    if unit_centres:
+        c /= np.linalg.norm(c, axis=1, keepdims=True)
+    pts = c[rng.integers(0, centres, count)] + noise * rng.standard_normal((count, dim))
+    return (pts / np.linalg.norm(pts, axis=1, keepdims=True)).astype(np.float32)
+
+
+def build_both(vectors, kw, metric, variants):
+    """generate_ann on the GPU under every config variant against one oracle build."""
+    from vectorlink_gpu.ann import generate_ann
+    cfg = oracle.make_config(**kw)
+    wb, wd, loops, found = oracle.generate_ann(vectors, cfg, metric=metric)
+    tv = t(vectors)
+    for extra in variants:
+        config = dict(cfg, **extra)
+        config["metric"] = metric
+        gb, gd = generate_ann(tv, config)
+        assert generate_ann.last_loops == loops, (extra, generate_ann.last_loops, loops)
+        assert np.array_equal(n(gb), wb), f"{extra}: neighbour ids differ from the oracle"
+        assert np.array_equal(n(gd), wd), f"{extra}: distances differ from the oracle"
+    return wb, wd, loops
+
+
+@pytest.mark.parametrize("batch_size", [10_000, 7_000])
+def test_config2_shaped_build_and_search_vs_oracle(batch_size, built_lib):
+    """Config 2's build shape (128-d, L2, degree 32, beam 64: graph width 96, 384 candidates per
+    iteration, search queue 96, visit queue 64, seen list 320) on a 20,000-vector draw, three rounds,
+    one batch per 10,000 rows and a split into three uneven batches; distance memo on, off and as the
+    build decides.  Then `.search` over that graph with the reference's 64 seeds and the widened scan."""
+    from vectorlink_gpu import ANN
+    rng = np.random.default_rng(2)
+    vectors = sift_like(rng, 20_000)
+    queries = sift_like(rng, 300)
+    kw = dict(beam_size=32, visit_queue_factor=2, recall_search_queue_factor=2, batch_size=batch_size)
+    wb, wd, loops = build_both(vectors, kw, "l2", [{}, {"memo": True}, {"memo": False}])
+    assert loops >= 2                                    # later rounds (memo, MAXINT tails) did run
+    for seed_factor in (1, 30):
+        skw = dict(kw, search_seed_factor=seed_factor) if seed_factor > 1 else kw
+        ann = ANN(t(vectors), beams=t(wb), distances=t(wd), metric="l2", **skw)
+        sq = ann.search(t(queries))
+        osq = oracle.search(vectors, wb, queries, oracle.make_config(**skw), metric="l2")
+        assert np.array_equal(n(sq.indices), osq.indices) and np.array_equal(n(sq.distances), osq.distances)
+
+
+@pytest.mark.parametrize("dim,count", [(768, 4000), (1024, 3000)])
+def test_config3_and_5_shaped_build_and_search_vs_oracle(dim, count, built_lib):
+    """Configs 3 and 5: 768-d / 1024-d unit vectors, cosine, degree 64, beam 128 - graph width 192,
+    768 candidates per iteration, search queue 192, visit queue 128, seen list 640, and the lane
+    layout that keeps the query in shared memory.  Two rounds; memo on and off."""
+    from vectorlink_gpu import ANN
+    rng = np.random.default_rng(dim)
+    vectors = embed_like(rng, count, dim, 40, 0.1 if dim == 768 else 0.05, unit_centres=(dim == 768))
+    queries = embed_like(rng, 64, dim, 40, 0.1 if dim == 768 else 0.05, unit_centres=(dim == 768))
+    vectors[1:40:8] = vectors[0:39:8]      # exact duplicates among the sampled rows: the self-recall check cannot
+    #                                        reach 1.0 (the copy with the smaller id wins the tie), so round two runs
+    kw = dict(beam_size=64, visit_queue_factor=2, recall_search_queue_factor=2, optimization_loops=2, batch_size=1500)
+    wb, wd, loops = build_both(vectors, kw, "cosine", [{"memo": True}, {"memo": False}])
+    assert loops == 2
+    ann = ANN(t(vectors), beams=t(wb), distances=t(wd), **kw)
+    sq = ann.search(t(queries))
+    osq = oracle.search(vectors, wb, queries, oracle.make_config(**kw))
+    assert np.array_equal(n(sq.indices), osq.indices) and np.array_equal(n(sq.distances), osq.distances)
+
+
+def test_experiment_runner_and_grid_search_write_logs(tmp_path, built_lib):
+    """The reference's runner (main.py) and its grid_search (ann.py:323-353) over the drop-in: a JSON
+    log per experiment carrying the build parameters, the timing and the self-recall."""
+    import importlib.util
+    import json
+    import os
+    from conftest import PKG_ROOT
+    from vectorlink_gpu.ann import grid_search
+    spec = importlib.util.spec_from_file_location("vl_runner", os.path.join(PKG_ROOT, "main.py"))
+    runner = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(runner)
+    path = runner.main(["-c", "1500", "-d", "64", "-n", "8", "-P", "-p", "4", "-r", "2", "-q", "2", "--seed", "1",
+                        "--log-dir", str(tmp_path / "log")])
+    log = json.load(open(path))
+    for key in ("prune", "beam_size", "parallel_visit_count", "total_time", "vector_count", "vector_dimension", "recall"):
+        assert key in log
+    assert log["vector_count"] == 1500 and log["vector_dimension"] == 64 and log["recall"] > 0.9
+    rng = np.random.default_rng(4)
+    logs = grid_search(t(unit(rng, 800, 32)), grid={"prune": [True, False], "beam_size": [6, 8]},
+                       base={"visit_queue_factor": 2, "recall_search_queue_factor": 2}, log_dir=str(tmp_path / "grid"))
+    assert len(logs) == 4 and len(os.listdir(tmp_path / "grid")) == 4
+    assert {(l["prune"], l["beam_size"]) for l in logs} == {(True, 6), (True, 8), (False, 6), (False, 8)}

@@ -59,3 +59,24 @@ def test_readme_alias_imports():
     from vectorlink.ann import ANN
     from vectorlink_gpu import ANN as ANN2
     assert ANN is ANN2
+
+
+def test_runner_flags_and_defaults_are_the_reference_runners():
+    """main.py:24-98 of the reference: same flags, and defaults that differ from ANN's own
+    (3 parallel visits, recall queue factor 6, pruning off unless -P)."""
+    import importlib.util
+    import os
+    from conftest import PKG_ROOT
+    spec = importlib.util.spec_from_file_location("vl_runner", os.path.join(PKG_ROOT, "main.py"))
+    runner = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(runner)
+    args = runner.make_parser().parse_args([])
+    params = runner.build_params(args)
+    assert params == {"vector_count": 10_000, "vector_dimension": 1536, "prune": False, "beam_size": 24,
+                      "parallel_visit_count": 3, "beam_queue_factor": 3, "visit_queue_factor": 3, "exclude_factor": 5,
+                      "optimization_loops": 3, "batch_size": 10_000, "recall_search_queue_factor": 6,
+                      "speculative_readahead": 5}
+    args = runner.make_parser().parse_args("-c 500 -d 64 -n 8 -P -p 4 -r 2 -q 2 -l 1 -L -C".split())
+    params = runner.build_params(args)
+    assert params["vector_count"] == 500 and params["prune"] is True and params["parallel_visit_count"] == 4
+    assert params["recall_search_queue_factor"] == 2 and params["optimization_loops"] == 1

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.abspath(os.path.join(HERE, "..", "include"))
 OUT = os.path.join(HERE, "vectorlink_gpu", "libvlgpu.so")
-SOURCES = ["vl_api.cu", "vl_distance.cu", "vl_queue.cu", "vl_prune.cu", "vl_symmetrize.cu", "vl_components.cu", "vl_beam.cu"]
+SOURCES = ["vl_api.cu", "vl_distance.cu", "vl_queue.cu", "vl_prune.cu", "vl_symmetrize.cu", "vl_components.cu", "vl_beam.cu", "vl_knn_tile.cu"]
 
 
 def _stale() -> bool:

@@ -23,7 +23,7 @@ EXPORTS = [
     "vl_last_error", "vl_abi_version", "vl_calculate_distances", "vl_search_from_seeds", "vl_queue_insert",
     "vl_queue_pop", "vl_punchout_excluded", "vl_dedup_adjacent", "vl_sort_pairs", "vl_dedup_sort_ids",
     "vl_seen_add", "vl_seen_add_noalloc", "vl_prune", "vl_prune_rows", "vl_reverse_edges", "vl_connected_components", "vl_beam_search",
-    "vl_beam_search_plan",
+    "vl_beam_search_plan", "vl_knn_prepare", "vl_knn_tile",
 ]
 
 
@@ -82,6 +82,8 @@ def lib() -> ctypes.CDLL:
         _lib.vl_prune_rows.argtypes = [P, P, L, I, L, L, I, P, P, I, P, P]
         _lib.vl_reverse_edges.argtypes = [P, L, I, I, I, P, P, P, P, I, P, P, P]
         _lib.vl_connected_components.argtypes = [P, P, L, I, L, ctypes.c_float, P, P, P]
+        _lib.vl_knn_prepare.argtypes = [P, L, I, P, I, P, P]
+        _lib.vl_knn_tile.argtypes = [P, L, I, P, L, L, L, L, I, P, P, P]
         _lib.vl_beam_search.argtypes = [ctypes.POINTER(BeamParams), P]
         _lib.vl_beam_search_plan.argtypes = [ctypes.POINTER(BeamParams), c_intp, c_intp, c_intp]
     return _lib

@@ -570,6 +570,36 @@ def ann_recall_test(vectors: Tensor, config: Dict):
     return ann_calculate_recall(vectors, beams, config, sample=vectors[:prefix])
 
 
+def grid_search(vectors: Optional[Tensor] = None, grid: Optional[Dict[str, list]] = None, base: Optional[Dict] = None,
+                log_dir: str = "./grid-log") -> List[Dict]:
+    """ann.py:323-353: one build + self-recall per point of a parameter grid, one JSON log per
+    point in `log_dir`.  Defaults are the reference's experiment: 1,000,000 random unit vectors of
+    1536 dimensions; prune x beam_size {24, 32, 46} x parallel_visit_count {1, 4} x
+    optimization_loops {1, 2} x visit_queue_factor {3, 4}.  (The reference's version calls an
+    undefined `main`; this one runs.)"""
+    import itertools
+    from .utils import generate_random_vectors
+    config = {"exclude_factor": 5, "batch_size": 10_000, "beam_queue_factor": 3, "recall_search_queue_factor": 6}
+    config.update(base or {})
+    if vectors is None:
+        vectors = generate_random_vectors(number_of_vectors=1_000_000, dimensions=1536)
+    if grid is None:
+        grid = {"prune": [True, False], "beam_size": [24, 32, 46], "parallel_visit_count": [1, 4],
+                "optimization_loops": [1, 2], "visit_queue_factor": [3, 4]}
+    os.makedirs(log_dir, exist_ok=True)
+    results = []
+    names = list(grid)
+    for point in itertools.product(*(grid[k] for k in names)):
+        kwargs = dict(config, **dict(zip(names, point)))
+        ann = ANN(vectors=vectors, **kwargs)
+        log = ann.dump_logs()
+        log["type"] = "cagra"
+        with open(os.path.join(log_dir, f"experiment-{time.time()}.log"), "w") as out:
+            json.dump(log, out)
+        results.append(log)
+    return results
+
+
 VERBOSE = bool(os.getenv("VECTORLINK_VERBOSE"))
 
 
@@ -585,7 +615,9 @@ class ANN:
     Added keywords: metric ("cosine" - the reference's distance on unit vectors - or "l2") and
     search_seed_factor (how many times Q seeds `.search` scans for its starting queue; 1 = the
     reference), prune_mode ("first" = the reference's detour test against y's first neighbour only,
-    "full" = against all of them), symmetrize (add reverse edges after the build; off = the reference) and group (a torch.distributed group whose ranks all pass the same vectors: the
+    "full" = against all of them), symmetrize (add reverse edges after the build; off = the reference),
+    init ("circulant" = the reference's start graph; "knn_tile" = exact-reranked proposals of a tensor-core
+    tile pass, see knn_tile.py) and group (a torch.distributed group whose ranks all pass the same vectors: the
     build's rows are split across them, see generate_ann)."""
 
     def __init__(self, vectors: Tensor, prune: bool = True, beam_size: int = 24, parallel_visit_count: int = 4,
@@ -593,7 +625,7 @@ class ANN:
                  optimization_loops: int = 3, batch_size: int = 10_000, recall_search_queue_factor: int = 3,
                  speculative_readahead: int = 5, beams: Optional[Tensor] = None, distances: Optional[Tensor] = None,
                  metric: str = "cosine", search_seed_factor: int = 1, group=None, symmetrize: bool = False,
-                 prune_mode: str = "first"):
+                 prune_mode: str = "first", init: str = "circulant"):
         (count, dim) = vectors.size()
         assert vectors.dtype == torch.float32
         _lib.require_cuda(vectors)
@@ -617,6 +649,9 @@ class ANN:
         assert prune_mode in ("first", "full")
         if prune_mode != "first":
             self.configuration["prune_mode"] = prune_mode
+        assert init in ("circulant", "knn_tile")
+        if init != "circulant":
+            self.configuration["init"] = init
         self.vectors = vectors.contiguous()
         wall_start = time.time()
         if beams is not None:

@@ -1,0 +1,102 @@
+"""Opt-in start graph from a tensor-core kNN tile pass (`ANN(init="knn_tile")`).
+
+The reference starts every build from a circulant graph (utils.py:35-41, ann.py:116-118):
+row i's first neighbours are rows i + p_j, i.e. arbitrary rows, and the first optimisation
+round spends its whole budget finding real neighbours.  This module proposes near neighbours
+with bf16 inner products on the tensor cores (csrc/vl_knn_tile.cu), then evaluates every proposed
+pair with the exact fp32 distance and orders the lists with the queue order, so the start
+graph holds exact distances and only real candidates; bf16 never reaches a list.
+
+Default builds do not come here: `init="circulant"` is the reference's behaviour.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import check, lib, ptr, stream_of
+from .constants import MAXFLOAT, MAXINT
+from .kernels import calculate_distances, metric_code, sort_pairs_
+from .log import nvtx_range
+
+TILE_K = 32            # VL_KNN_TILE_K: proposals per row and candidate segment
+BLOCK_K = 64           # the bf16 copy is padded to a multiple of this many columns
+
+
+def prepare(vectors: Tensor, want_norms: bool) -> Tuple[Tensor, Optional[Tensor]]:
+    """bf16 copy of the rows, zero-padded to a multiple of 64 columns, and |row|^2 (fp32) when asked."""
+    _lib.require_cuda(vectors)
+    assert vectors.dtype == torch.float32 and vectors.is_contiguous()
+    (n, dim) = vectors.size()
+    dim_pad = (dim + BLOCK_K - 1) // BLOCK_K * BLOCK_K
+    rows_bf16 = torch.empty((n, dim_pad), dtype=torch.bfloat16, device=vectors.device)
+    norms = torch.empty(n, dtype=torch.float32, device=vectors.device) if want_norms else None
+    check(lib().vl_knn_prepare(ptr(vectors), ctypes.c_int64(n), dim, ptr(rows_bf16), dim_pad, ptr(norms),
+                               stream_of(vectors)), "vl_knn_prepare")
+    return rows_bf16, norms
+
+
+def proposals(rows_bf16: Tensor, norms: Optional[Tensor], rows: Tuple[int, int], candidates: Tuple[int, int],
+              segments: int) -> Tensor:
+    """int32 [rows, segments * 32]: per row the 32 best-scoring candidate ids of each of `segments`
+    equal parts of the candidate range (approximate scores; the row itself excluded), MAXINT-padded."""
+    _lib.require_cuda(rows_bf16, norms)
+    assert rows_bf16.dtype == torch.bfloat16 and rows_bf16.is_contiguous()
+    (n, dim_pad) = rows_bf16.size()
+    (lo, hi) = rows
+    out = torch.empty((hi - lo, segments * TILE_K), dtype=torch.int32, device=rows_bf16.device)
+    check(lib().vl_knn_tile(ptr(rows_bf16), ctypes.c_int64(n), dim_pad, ptr(norms), ctypes.c_int64(lo), ctypes.c_int64(hi),
+                            ctypes.c_int64(candidates[0]), ctypes.c_int64(candidates[1]), segments, ptr(out),
+                            ptr(_lib.status_word(rows_bf16.device)), stream_of(rows_bf16)), "vl_knn_tile")
+    return out
+
+
+def exact_lists(vectors: Tensor, ids: Tensor, row_lo: int, width: int, metric: str) -> Tuple[Tensor, Tensor]:
+    """The fp32 rerank: exact distances of the proposed pairs (the same summation tree as every
+    other distance), rows put in queue order with repeats removed, cut or MAXINT-padded to `width`."""
+    rows = ids.size(0)
+    dist = calculate_distances(vectors, ids, metric=metric, queries=vectors[row_lo:row_lo + rows])
+    sort_pairs_(ids, dist, dedup=True)
+    if ids.size(1) >= width:
+        return ids[:, :width].contiguous(), dist[:, :width].contiguous()
+    out_i = torch.full((rows, width), MAXINT, dtype=torch.int32, device=ids.device)
+    out_d = torch.full((rows, width), MAXFLOAT, dtype=torch.float32, device=ids.device)
+    out_i[:, : ids.size(1)] = ids
+    out_d[:, : ids.size(1)] = dist
+    return out_i, out_d
+
+
+def knn_start_graph(vectors: Tensor, width: int, config: Dict, group=None) -> Tuple[Tensor, Tensor]:
+    """Start graph [N, width] (ids, exact distances) for generate_ann.  config["knn_segments"]
+    (default ceil(width / 32)) parts of the row range each contribute their 32 best proposals per
+    row.  With `group`, each rank computes the lists of its share of the rows and the lists are
+    all-gathered (every rank holds all vectors)."""
+    (n, dim) = vectors.size()
+    metric = config.get("metric", "cosine")
+    segments = int(config.get("knn_segments", 0)) or max(1, (width + TILE_K - 1) // TILE_K)
+    world, rank = 1, 0
+    if group is not None:
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+    per = (n + world - 1) // world
+    lo, hi = min(n, rank * per), min(n, (rank + 1) * per)
+    with nvtx_range("vl.knn_tile.prepare"):
+        rows_bf16, norms = prepare(vectors, want_norms=metric_code(metric) == 1)
+    beams = torch.empty((world * per, width), dtype=torch.int32, device=vectors.device)
+    dists = torch.empty((world * per, width), dtype=torch.float32, device=vectors.device)
+    if hi > lo:
+        with nvtx_range("vl.knn_tile.proposals"):
+            ids = proposals(rows_bf16, norms, (lo, hi), (0, n), segments)
+        with nvtx_range("vl.knn_tile.rerank"):
+            (b, d) = exact_lists(vectors, ids, lo, width, metric)
+        beams[lo:hi] = b
+        dists[lo:hi] = d
+    if world > 1:
+        from .ann import _gather_row_blocks
+        _gather_row_blocks(beams, per, group)
+        _gather_row_blocks(dists, per, group)
+    return beams[:n], dists[:n]
