@@ -302,6 +302,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--loops", type=int, default=0, help="override optimization_loops")
     ap.add_argument("--quick", action="store_true", help="skip the host-buffer pass and the recall evaluation")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip only the host-buffer pass (long single builds)")
+    ap.add_argument("--init", default="circulant", choices=["circulant", "knn_tile"],
+                    help="start graph of the build: the reference's circulant graph (default) or the tensor-core tile pass")
+    ap.add_argument("--mode", default="rows", choices=["rows", "shards"], help="multi-GPU build mode (see sharded.py)")
     args = ap.parse_args()
     name = args.workload
     w = dict(WORKLOADS[name])
@@ -331,6 +335,8 @@ def main():
     kw = ann_kwargs(w)
     if args.loops:
         kw["optimization_loops"] = args.loops
+    if args.init != "circulant":
+        kw["init"] = args.init
     # strong scaling: the job is always the workload's w["n"] vectors; rank r starts with rows
     # [lo_r, hi_r) of them in its HBM.  A step all-gathers the shards and runs the build with every
     # round's rows split across the ranks (ShardedANN mode "rows"): the graph is bit-identical to
@@ -357,7 +363,7 @@ def main():
 
     def build(v):
         if world > 1:
-            return ShardedANN(v, group=dist.group.WORLD, mode="rows", **kw)
+            return ShardedANN(v, group=dist.group.WORLD, mode=args.mode, **kw)
         return ANN(vectors=v, **kw)
 
     def step_device():
@@ -398,16 +404,17 @@ def main():
 
     # end to end with host buffers
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if not args.quick:
+    do_e2e = not (args.quick or args.skip_e2e)
+    if do_e2e:
         step_e2e()
         barrier()
     e0.record()
-    if not args.quick:
+    if do_e2e:
         for _ in range(args.steps):
             step_e2e()
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1) if not args.quick else float("nan")
+    e2e_ms = e0.elapsed_time(e1) if do_e2e else float("nan")
 
     # search over the built graph (data-parallel over the ranks when there are several)
     def do_search():
@@ -459,9 +466,13 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": name, "vectors": total, "vectors_per_gpu": n, "dim": dim, **kw, "loops_run": vl_ann.generate_ann.last_loops,
                        "l2_policy": "inputs (vectors %d MB + graph) exceed the 126 MB L2" % (total * dim * 4 // 2**20),
-                       "sharding": ("vectors all-gathered, each round's rows split across ranks, new neighbour lists "
-                                    "broadcast per round (NCCL)") if world > 1 else "none"},
-            "e2e": {"value": total / (e2e_ms / args.steps * 1e-3), "unit": "vectors/s",
+                       "sharding": ("none" if world == 1 else
+                                    ("vectors all-gathered; each round's rows split evenly across ranks, searched and pruned "
+                                     "by their rank, lists all-gathered (NCCL): the single-GPU graph") if args.mode == "rows" else
+                                    ("each rank builds the graph of its own shard, then a merge pass: rows all-gathered "
+                                     "chunk by chunk, every shard searched for the foreign rows, candidate lists "
+                                     "all-gathered and merged by the owner (NCCL)"))},
+            "e2e": {"value": (total / (e2e_ms / args.steps * 1e-3)) if e2e_ms == e2e_ms else None, "unit": "vectors/s",
                     "h2d_bytes_per_step": total * dim * 4, "d2h_bytes_per_step": total * kw["beam_size"] * 8},
             "gpu_launches": launches,
             "search": {"qps": queries.size(0) / (search_ms * 1e-3), "queries": queries.size(0), "k": 10,

@@ -45,33 +45,37 @@ def test_prepare_rounds_to_bf16_pads_and_sums_squares(built_lib):
 
 
 @pytest.mark.parametrize("count,segments,rows", [(1000, 1, (0, 1000)), (2500, 3, (300, 1700)), (130, 2, (0, 130))])
-def test_proposals_are_the_exact_top_of_every_segment_on_integer_data(count, segments, rows, built_lib):
+def test_proposals_are_the_exact_top_of_every_list_on_integer_data(count, segments, rows, built_lib):
     """Integer-valued rows below 256 are exact in bf16 and their inner products are exact in the fp32
-    accumulator, so the proposed ids must be exactly the 32 nearest (squared L2, ties by id) of each
-    candidate segment, the row itself left out."""
+    accumulator, so every list must hold exactly the 32 nearest (squared L2, ties by id) of its
+    candidates - the even or the odd 128-candidate tiles of its segment - the row itself left out."""
     from vectorlink_gpu.knn_tile import prepare, proposals
     rng = np.random.default_rng(count)
     v = sift_like(rng, count)
     rows_bf16, norms = prepare(t(v), want_norms=True)
     got = n(proposals(rows_bf16, norms, rows, (0, count), segments))
     assert status_clear()
+    assert got.shape == (rows[1] - rows[0], segments * 64)
     per_segment = (count + segments - 1) // segments
     seg_len = (per_segment + 127) // 128 * 128                 # the kernel cuts the range at multiples of 128
     d = ((v[rows[0]:rows[1], None, :].astype(np.float64) - v[None, :, :].astype(np.float64)) ** 2).sum(2)
     d[np.arange(rows[1] - rows[0]), np.arange(rows[0], rows[1])] = np.inf
+    ids = np.arange(count)
     for s in range(segments):
         lo, hi = s * seg_len, min(count, (s + 1) * seg_len)
-        part = got[:, s * 32:(s + 1) * 32]
-        if hi <= lo:
-            assert (part == MAXINT).all()
-            continue
-        keep = min(32, hi - lo)
-        order = np.lexsort((np.broadcast_to(np.arange(lo, hi), d[:, lo:hi].shape), d[:, lo:hi]), axis=1)[:, :keep] + lo
-        finite = np.take_along_axis(d, order, 1) < np.inf          # a segment of fewer than 33 rows may hold the row itself
-        for r in range(got.shape[0]):
-            want = order[r][finite[r]]
-            assert np.array_equal(part[r, :len(want)], want), (s, r)
-            assert (part[r, len(want):] == MAXINT).all()
+        for parity in (0, 1):
+            part = got[:, (2 * s + parity) * 32:(2 * s + parity + 1) * 32]
+            members = ids[(ids >= lo) & (ids < hi) & ((((ids - lo) // 128) & 1) == parity)]
+            if len(members) == 0:
+                assert (part == MAXINT).all()
+                continue
+            dm = d[:, members]
+            order = members[np.lexsort((np.broadcast_to(members, dm.shape), dm), axis=1)[:, :32]]
+            finite = np.take_along_axis(d, order, 1) < np.inf      # a short list may reach the row itself
+            for r in range(got.shape[0]):
+                want = order[r][finite[r]]
+                assert np.array_equal(part[r, :len(want)], want), (s, parity, r)
+                assert (part[r, len(want):] == MAXINT).all()
 
 
 @pytest.mark.parametrize("dim,metric", [(96, "cosine"), (768, "cosine"), (1024, "cosine"), (128, "l2")])

@@ -295,3 +295,21 @@ def test_full_prune_scan_vs_numpy(built_lib):
     assert np.array_equal(n(gb), wb) and np.array_equal(n(gd), wd)
     fb, _ = prune_(t(order), t(d))
     assert (n(gb) == MAXINT).sum() > (n(fb) == MAXINT).sum()       # prunes more than the first-neighbour test
+
+
+def test_prune_of_a_row_range_equals_the_full_prune_on_those_rows(built_lib):
+    """vl_prune_rows: witnesses are read from every row, only the rows of the range are written."""
+    from vectorlink_gpu.kernels import prune_
+    rng = np.random.default_rng(33)
+    rows, w = 500, 12
+    v = unit(rng, rows, 8)
+    kn = oracle.bruteforce_knn(v, v, w, exclude_self=True)
+    d = oracle.calculate_distances(v, kn)
+    full_b, full_d = prune_(t(kn), t(d))
+    out_b = torch.full((rows, w), -7, dtype=torch.int32, device=DEV)
+    out_d = torch.full((rows, w), -7.0, dtype=torch.float32, device=DEV)
+    prune_(t(kn), t(d), rows=(123, 377), out=(out_b, out_d))
+    assert torch.equal(out_b[123:377], full_b[123:377]) and torch.equal(out_d[123:377], full_d[123:377])
+    assert bool((out_b[:123] == -7).all()) and bool((out_b[377:] == -7).all())
+    wb, wd = oracle.prune_(kn, d)
+    assert np.array_equal(n(full_b), wb) and np.array_equal(n(full_d), wd)

@@ -10,16 +10,25 @@
 // distances as everything else; bf16 only decides which pairs get that exact evaluation.
 //
 // Shape of the kernel (one CTA per SM, persistent over work items = row tile x candidate segment):
-//   warp 0, one lane : TMA producer - cp.async.bulk.tensor 2D loads of the row tile's and the
-//                      candidate tile's 64-column k-block (128 B rows, 128B swizzle) into a
-//                      4-stage shared-memory ring, completion on an mbarrier per stage;
+//   warp 0, one lane : TMA producer - cp.async.bulk.tensor 2D loads of 64-column k-blocks (128 B
+//                      rows, 128B swizzle) into a shared-memory ring, completion on an mbarrier
+//                      per stage.  Rows of at most 256 padded columns keep the row tile resident
+//                      (loaded once per work item) and stream only candidate tiles (4 stages of
+//                      16 KB); longer rows stream both operands (3 stages of 32 KB);
 //   warp 1, one lane : issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32, M=128, N=128, K=16)
 //                      from shared-memory descriptors into one of two TMEM accumulators
 //                      (128 columns each), tcgen05.commit releases the stage / publishes the tile;
-//   warps 2..5       : read their quarter of the accumulator's 128 lanes with tcgen05.ld (one
-//                      row per thread), turn inner products into scores and keep the row's
-//                      32 best (score, id) keys in registers; the accumulator is handed back as
-//                      soon as it is read, so the next tile's MMAs overlap the selection.
+//   warps 2..9       : two groups of four.  Group g owns accumulator g, i.e. every second candidate
+//                      tile of a segment, and keeps its own lists, so a row ends up with two lists
+//                      per segment (the best of the even tiles and the best of the odd tiles) and
+//                      two warps per scheduler hide each other's latencies.  A warp reads
+//                      its quarter of the accumulator's 128 lanes with tcgen05.ld (one
+//                      row per thread, the next 32 columns in flight while 32 are examined),
+//                      turn inner products into scores and keep each row's 32 best (score, id)
+//                      keys in shared memory, one key per lane: three instructions per column
+//                      mark the few that beat the row's worst key, and each of those is inserted
+//                      by the whole warp with one ballot and one shuffle; the accumulator is
+//                      handed back as soon as it is read, so the next tile's MMAs overlap this.
 // No load uses cluster multicast, no thread-block cluster is launched.
 //
 // Every wait (mbarrier phases) is bounded by wall time: when a wait runs out the kernel sets
@@ -35,21 +44,30 @@ namespace {
 constexpr int kTileRows = 128;                 // M of the MMA: rows of the row tile
 constexpr int kTileCands = 128;                // N of the MMA: candidates per tile
 constexpr int kBlockK = 64;                    // bf16 elements per k-block = one 128-byte swizzle row
-constexpr int kStages = 4;
-constexpr int kTopK = VL_KNN_TILE_K;           // keys kept per row and segment
-constexpr int kThreads = 192;                  // warp 0 producer, warp 1 MMA, warps 2-5 selection
-constexpr uint32_t kTileBytes = kTileRows * kBlockK * 2;              // 16 KB per operand per stage
-constexpr uint32_t kStageBytes = 2 * kTileBytes;
+constexpr int kMaxStages = 4;                  // barrier slots; resident mode uses 4 stages, streaming mode 3
+constexpr int kResidentKBlocks = 4;            // row tiles of up to 4 k-blocks (256 columns) stay in shared memory
+constexpr int kTopK = VL_KNN_TILE_K;           // keys per list
+constexpr int kLists = VL_KNN_TILE_LISTS;      // lists per row and segment: one per selection group
+constexpr int kThreads = 320;                  // warp 0 producer, warp 1 MMA, warps 2-9 selection (two groups of four)
+constexpr uint32_t kTileBytes = kTileRows * kBlockK * 2;              // 16 KB: one operand's k-block
+// operand region, 128 KB: resident mode = 4 candidate stages of 16 KB + the row tile's 4 k-blocks;
+// streaming mode = 3 stages of (candidates + rows) 32 KB
+constexpr uint32_t kOperandBytes = 8 * kTileBytes;
+constexpr uint32_t kOffRowTile = 4 * kTileBytes;
 constexpr uint32_t kTmemCols = 2 * kTileCands;                         // two accumulators
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;             // 2 s per wait
 
 // shared-memory layout behind the 1024-byte aligned base
-constexpr uint32_t kOffBars = kStages * kStageBytes;                   // full[4] empty[4] tfull[2] tempty[2] drain[1]
-constexpr uint32_t kOffSlot = kOffBars + 8 * (2 * kStages + 5);        // TMEM base address written by tcgen05.alloc
+constexpr uint32_t kOffBars = kOperandBytes;
+// full[4] empty[4] tfull[2] tempty[2] drain rows_full rows_empty
+constexpr uint32_t kOffSlot = kOffBars + 8 * (2 * kMaxStages + 7);     // TMEM base address written by tcgen05.alloc
 constexpr uint32_t kOffAbort = kOffSlot + 4;
-constexpr uint32_t kOffBias = (kOffAbort + 4 + 127) & ~127u;           // [4 warps][2 buffers][128] floats
-constexpr uint32_t kOffPend = kOffBias + 4 * 2 * kTileCands * 4;      // [32 slots][128 rows] keys waiting for insertion
-constexpr uint32_t kSmemBytes = kOffPend + 32 * kTileRows * 8 + 1024;  // + slack for the alignment
+constexpr uint32_t kOffBias = (kOffAbort + 4 + 127) & ~127u;           // [8 warps][128] floats: score offsets of a warp's current tile
+constexpr uint32_t kOffLists = kOffBias + 8 * kTileCands * 4;          // [2 groups][128 rows][32] best keys of the work item
+constexpr uint32_t kSmemBytes = kOffLists + kLists * kTileRows * kTopK * 8 + 1024;   // + slack for the alignment
+static_assert(kTopK == 32, "a row's list is held one key per lane");
+static_assert(kLists == 2, "one list per accumulator");
+static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -145,6 +163,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
 // kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N=128, M=128
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileCands >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
 
+#ifdef VL_KNN_STATS
+#define VL_T0() const long long t_begin__ = clock64()
+#define VL_T1(slot) do { if (a.stats) atomicAdd(a.stats + (slot), (unsigned long long)(clock64() - t_begin__)); } while (0)
+#else
+#define VL_T0() do {} while (0)
+#define VL_T1(slot) do {} while (0)
+#endif
+
 struct KnnArgs {
     const float* bias;        // |c|^2 per candidate row (squared L2) or nullptr (cosine)
     int64_t n;                // rows of the bf16 matrix
@@ -153,32 +179,58 @@ struct KnnArgs {
     int64_t cand_lo, cand_hi; // candidates offered to every row
     int segments;             // the candidate range is cut into this many parts, each with its own top-k
     int64_t seg_len;          // candidates per part (a multiple of 128)
-    int32_t* out_ids;         // [row_hi - row_lo, segments * kTopK]
+    int32_t* out_ids;         // [row_hi - row_lo, segments, kLists, kTopK]
     int* status;
+    unsigned long long* stats; // cycle counters of a profiling build (-DVL_KNN_STATS), else unused
 };
 
+// v[j] for a j that is the same in every lane of the warp: a jump on j (register arrays cannot be
+// indexed at run time; the branch is uniform, so it costs one case, not thirty-two)
+__device__ __forceinline__ uint32_t pick32(const uint32_t (&v)[32], int j)
+{
+    uint32_t x = 0;
+    switch (j) {
+#define VL_PICK(i) case i: x = v[i]; break;
+        VL_PICK(0) VL_PICK(1) VL_PICK(2) VL_PICK(3) VL_PICK(4) VL_PICK(5) VL_PICK(6) VL_PICK(7)
+        VL_PICK(8) VL_PICK(9) VL_PICK(10) VL_PICK(11) VL_PICK(12) VL_PICK(13) VL_PICK(14) VL_PICK(15)
+        VL_PICK(16) VL_PICK(17) VL_PICK(18) VL_PICK(19) VL_PICK(20) VL_PICK(21) VL_PICK(22) VL_PICK(23)
+        VL_PICK(24) VL_PICK(25) VL_PICK(26) VL_PICK(27) VL_PICK(28) VL_PICK(29) VL_PICK(30) VL_PICK(31)
+#undef VL_PICK
+    }
+    return x;
+}
+
+// RESIDENT: the row tile (all its k-blocks) is loaded once per work item and only candidate
+// tiles go through the ring; otherwise a ring stage holds one k-block of both operands.
+template <bool RESIDENT>
 __global__ void __launch_bounds__(kThreads, 1)
 knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
 {
+    constexpr uint32_t kStages = RESIDENT ? 4 : 3;
+    constexpr uint32_t kStageBytes = RESIDENT ? kTileBytes : 2 * kTileBytes;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - raw);
     const uint32_t bar_full = base + kOffBars;                    // + 8 * stage
-    const uint32_t bar_empty = bar_full + 8 * kStages;
-    const uint32_t bar_tfull = bar_empty + 8 * kStages;           // + 8 * accumulator
+    const uint32_t bar_empty = bar_full + 8 * kMaxStages;
+    const uint32_t bar_tfull = bar_empty + 8 * kMaxStages;        // + 8 * accumulator
     const uint32_t bar_tempty = bar_tfull + 16;
     const uint32_t bar_drain = bar_tempty + 16;
+    const uint32_t bar_rows_full = bar_drain + 8;                 // resident row tile landed
+    const uint32_t bar_rows_empty = bar_rows_full + 8;            // every MMA that reads it has finished
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kOffSlot);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffAbort);
     float* bias_smem = reinterpret_cast<float*>(base_ptr + kOffBias);
-    vl_key_t* pend_smem = reinterpret_cast<vl_key_t*>(base_ptr + kOffPend);
+    vl_key_t* lists_smem = reinterpret_cast<vl_key_t*>(base_ptr + kOffLists);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 4); }
         mbar_init(bar_drain, 1);
+        mbar_init(bar_rows_full, 1);
+        mbar_init(bar_rows_empty, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -197,7 +249,7 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
-        uint32_t it = 0;
+        uint32_t it = 0, nres = 0;                                  // nres: work items with a non-empty candidate range so far
         bool ok = true;
 #pragma unroll 1
         for (int64_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
@@ -205,16 +257,25 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
             const int64_t row0 = a.row_lo + rt * kTileRows;
             const int64_t c_begin = a.cand_lo + seg * a.seg_len;
             const int64_t c_end = (c_begin + a.seg_len < a.cand_hi) ? c_begin + a.seg_len : a.cand_hi;
+            if (RESIDENT && c_begin < c_end) {
+                // the previous item's MMAs must be done with the row tile before it is overwritten
+                ok = mbar_wait(bar_rows_empty, (nres & 1u) ^ 1u, abort_flag, a.status);
+                if (!ok) break;
+                ++nres;
+                mbar_expect_tx(bar_rows_full, a.kblocks * kTileBytes);
+                for (int kb = 0; kb < a.kblocks; ++kb)
+                    tma_load_2d(base + kOffRowTile + kb * kTileBytes, &tmap, kb * kBlockK, (int)row0, bar_rows_full);
+            }
 #pragma unroll 1
             for (int64_t c0 = c_begin; c0 < c_end && ok; c0 += kTileCands) {
 #pragma unroll 1
                 for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status);
+                    { VL_T0(); ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status); VL_T1(0); }
                     if (!ok) break;
                     mbar_expect_tx(bar_full + 8 * s, kStageBytes);
-                    tma_load_2d(base + s * kStageBytes, &tmap, kb * kBlockK, (int)row0, bar_full + 8 * s);
-                    tma_load_2d(base + s * kStageBytes + kTileBytes, &tmap, kb * kBlockK, (int)c0, bar_full + 8 * s);
+                    if (!RESIDENT) tma_load_2d(base + s * kStageBytes + kTileBytes, &tmap, kb * kBlockK, (int)row0, bar_full + 8 * s);
+                    tma_load_2d(base + s * kStageBytes, &tmap, kb * kBlockK, (int)c0, bar_full + 8 * s);
                 }
             }
         }
@@ -229,28 +290,38 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
-        uint32_t it = 0, tile = 0;
+        uint32_t it = 0, nres = 0, used0 = 0, used1 = 0;            // tiles accumulator 0 / 1 has held so far
         bool ok = true;
 #pragma unroll 1
         for (int64_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
             const int64_t seg = item % a.segments;
             const int64_t c_begin = a.cand_lo + seg * a.seg_len;
             const int64_t c_end = (c_begin + a.seg_len < a.cand_hi) ? c_begin + a.seg_len : a.cand_hi;
+            if (RESIDENT && c_begin < c_end) {
+                ok = mbar_wait(bar_rows_full, nres & 1u, abort_flag, a.status);
+                if (!ok) break;
+                ++nres;
+                tc_fence_after();
+            }
+            uint32_t lt = 0;                                        // tile index within the segment: its parity picks the accumulator
 #pragma unroll 1
-            for (int64_t c0 = c_begin; c0 < c_end && ok; c0 += kTileCands, ++tile) {
-                const uint32_t buf = tile & 1u, tph = (tile >> 1) & 1u;
-                ok = mbar_wait(bar_tempty + 8 * buf, tph ^ 1u, abort_flag, a.status);   // accumulator drained?
+            for (int64_t c0 = c_begin; c0 < c_end && ok; c0 += kTileCands, ++lt) {
+                const uint32_t buf = lt & 1u;
+                const uint32_t tph = (buf ? used1 : used0) & 1u;
+                if (buf) ++used1; else ++used0;
+                { VL_T0(); ok = mbar_wait(bar_tempty + 8 * buf, tph ^ 1u, abort_flag, a.status); VL_T1(1); }   // accumulator drained?
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * kTileCands;
 #pragma unroll 1
                 for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status);
+                    { VL_T0(); ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status); VL_T1(2); }
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t a_desc = smem_desc_sw128(base + s * kStageBytes);
-                    const uint64_t b_desc = smem_desc_sw128(base + s * kStageBytes + kTileBytes);
+                    const uint64_t a_desc = smem_desc_sw128(RESIDENT ? base + kOffRowTile + kb * kTileBytes
+                                                                     : base + s * kStageBytes + kTileBytes);
+                    const uint64_t b_desc = smem_desc_sw128(base + s * kStageBytes);
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)      // 16 bf16 = 32 bytes = 2 descriptor units per step
                         tc_mma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, (kb | kk) != 0);
@@ -258,6 +329,7 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
                 }
                 if (ok) tc_commit(bar_tfull + 8 * buf);            // accumulator complete
             }
+            if (RESIDENT && ok && c_begin < c_end) tc_commit(bar_rows_empty);   // row tile free once this item's MMAs are done
         }
         // every MMA issued above must have finished before the TMEM columns are given back
         tc_commit(bar_drain);
@@ -267,10 +339,12 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
         }
     } else if (warp >= 2) {
         // ---------------- selection: one row of the tile per thread ----------------
+        const int group = (warp - 2) >> 2;                         // 0: even tiles of a segment (accumulator 0), 1: odd tiles
         const int quarter = warp & 3;                              // the TMEM lanes this warp may read
         const int row_in_tile = quarter * 32 + lane;
-        float* my_bias = bias_smem + (warp - 2) * 2 * kTileCands;
-        uint32_t tile = 0;
+        float* bias_tile = bias_smem + (warp - 2) * kTileCands;
+        const float kInf = __int_as_float(0x7f800000);
+        uint32_t used = 0;                                         // tiles this group's accumulator has held so far
         bool ok = true;
 #pragma unroll 1
         for (int64_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
@@ -278,69 +352,121 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
             const int64_t row = a.row_lo + rt * kTileRows + row_in_tile;
             const int64_t c_begin = a.cand_lo + seg * a.seg_len;
             const int64_t c_end = (c_begin + a.seg_len < a.cand_hi) ? c_begin + a.seg_len : a.cand_hi;
-            // the row's best keys so far, ascending, in registers; `worst` = score of the last one
-            vl_key_t top[kTopK];
+            // The 32 best keys of each of this warp's 32 rows, ascending, in shared memory: row r's list is
+            // warp_lists[r * 32 + lane], one key per lane, so that an insertion is a warp-wide shift (a few
+            // instructions) instead of a 32-step register sort by the one lane that owns the row.  Each
+            // lane keeps `worst`, the score of its own row's last key (+inf until the list is full).
+            vl_key_t* warp_lists = lists_smem + ((size_t)group * kTileRows + quarter * 32) * kTopK;
+            __syncwarp();
 #pragma unroll
-            for (int j = 0; j < kTopK; ++j) top[j] = ~0ull;
-            float worst = __int_as_float(0x7f800000);             // +inf until the list is full
-            vl_key_t* pend = pend_smem + row_in_tile;              // slot p of this row at pend[p * kTileRows]
+            for (int r = 0; r < 32; ++r) warp_lists[r * kTopK + lane] = ~0ull;
+            __syncwarp();
+            float worst = kInf;
+
+            // Examines 32 accumulator columns: three instructions per column on the common path (score,
+            // compare, mark); when no lane marked anything the chunk is done.  Otherwise every marked
+            // (row, column) is inserted into its row's list by the whole warp.
+            auto examine = [&](const uint32_t (&v)[32], const float* bias32, int64_t col0) {
+                // four independent partial masks: the chain of dependent instructions has to stay short
+                uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
+#pragma unroll
+                for (int j4 = 0; j4 < 32; j4 += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bias32 + j4);
+                    m0 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 0]), b4.x) < worst) ? (1u << (j4 + 0)) : 0u;
+                    m1 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 1]), b4.y) < worst) ? (1u << (j4 + 1)) : 0u;
+                    m2 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 2]), b4.z) < worst) ? (1u << (j4 + 2)) : 0u;
+                    m3 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 3]), b4.w) < worst) ? (1u << (j4 + 3)) : 0u;
+                }
+                const uint32_t marks = (m0 | m1) | (m2 | m3);
+                // columns marked by any row of the warp (usually none, one or two): the loop below is over
+                // those only, and is kept rolled so that the code stays small
+                uint32_t cols = __reduce_or_sync(0xffffffffu, marks);
 #pragma unroll 1
-            for (int64_t c0 = c_begin; c0 < c_end; c0 += kTileCands, ++tile) {
-                const uint32_t buf = tile & 1u, tph = (tile >> 1) & 1u;
-                // this warp's copy of the tile's score offsets: |c|^2 (squared L2) or 0 (cosine), +inf past the
-                // segment's end so that such a column never qualifies (warp-local: this role uses no CTA-wide barrier)
+                while (cols) {
+                    const int j = __ffs(cols) - 1;                  // the same for every lane
+                    cols &= cols - 1;
+                    const float score = fmaf(-2.0f, __uint_as_float(pick32(v, j)), bias32[j]);
+                    const vl_key_t my_key = ((vl_key_t)vl_ord(score) << 32) | (uint32_t)(col0 + j);
+                    // `worst` may have fallen since the marks were taken; a row never lists itself
+                    unsigned live = __ballot_sync(0xffffffffu, ((marks >> j) & 1u) && score < worst && col0 + j != row);
+#pragma unroll 1
+                    while (live) {
+                        const int owner = __ffs(live) - 1;
+                        live &= live - 1;
+                        const vl_key_t key = __shfl_sync(0xffffffffu, my_key, owner);
+                        vl_key_t* lst = warp_lists + owner * kTopK;
+                        const vl_key_t e = lst[lane];
+                        const int pos = __popc(__ballot_sync(0xffffffffu, e < key));    // sorted: the smaller keys are a prefix
+                        const vl_key_t prev = __shfl_up_sync(0xffffffffu, e, 1);
+                        const vl_key_t ne = lane < pos ? e : (lane == pos ? key : prev);
+                        lst[lane] = ne;
+                        const vl_key_t tail = __shfl_sync(0xffffffffu, ne, 31);
+                        if (lane == owner && tail != ~0ull) worst = vl_unord((uint32_t)(tail >> 32));
+                        __syncwarp();
+                    }
+                }
+            };
+
+            // score offsets of a tile, four columns per lane: |c|^2 (squared L2) or 0 (cosine), +inf past the
+            // segment's end so that such a column never qualifies
+            auto load_bias = [&](int64_t c0, float (&b)[4]) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int64_t c = c0 + lane + 32 * q;
+                    b[q] = (c < c_end) ? (a.bias ? __ldg(a.bias + c) : 0.0f) : kInf;
+                }
+            };
+            float next_bias[4];
+            const int64_t c_first = c_begin + (int64_t)group * kTileCands;
+            if (c_first < c_end) load_bias(c_first, next_bias);
+#pragma unroll 1
+            for (int64_t c0 = c_first; c0 < c_end; c0 += 2 * kTileCands) {
+                // this warp's own copy of the offsets (warp-local: this role uses no CTA-wide barrier); the
+                // next tile's offsets are requested now and stored when this tile is done
                 __syncwarp();
 #pragma unroll
-                for (int j = lane; j < kTileCands; j += 32)
-                    my_bias[buf * kTileCands + j] = (c0 + j < c_end) ? (a.bias ? __ldg(a.bias + c0 + j) : 0.0f)
-                                                                     : __int_as_float(0x7f800000);
+                for (int q = 0; q < 4; ++q) bias_tile[lane + 32 * q] = next_bias[q];
                 __syncwarp();
-                ok = mbar_wait(bar_tfull + 8 * buf, tph, abort_flag, a.status);
+                if (c0 + 2 * kTileCands < c_end) load_bias(c0 + 2 * kTileCands, next_bias);
+                const uint32_t tph = used & 1u;
+                ++used;
+                { VL_T0(); ok = mbar_wait(bar_tfull + 8 * group, tph, abort_flag, a.status); if (lane == 0 && warp == 2) VL_T1(3); }
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kTileCands;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + group * kTileCands;
+                uint32_t v0[32], v1[32];
+                VL_T0();
+                tc_load32(taddr, v0);
+                tc_wait_ld();
+                if (lane == 0 && warp == 2) VL_T1(4);
 #pragma unroll 1
-                for (int ch = 0; ch < kTileCands / 32; ++ch) {
-                    uint32_t v[32];
-                    __syncwarp();                                   // the loads below are warp-collective
-                    tc_load32(taddr + ch * 32, v);
+                for (int ch = 0; ch < kTileCands / 32; ch += 2) {
+                    __syncwarp();                                   // the loads are warp-collective
+                    tc_load32(taddr + (ch + 1) * 32, v1);           // in flight while v0 is examined
+                    examine(v0, bias_tile + ch * 32, c0 + ch * 32);
+                    __syncwarp();
                     tc_wait_ld();
-                    // pass 1 (unrolled, a few instructions per column): which columns beat the row's worst key
-                    int n_pend = 0;
-                    const float* bias_ch = my_bias + buf * kTileCands + ch * 32;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float score = fmaf(-2.0f, __uint_as_float(v[j]), bias_ch[j]);
-                        if (score < worst) {
-                            pend[n_pend * kTileRows] = ((vl_key_t)vl_ord(score) << 32) | (uint32_t)(c0 + ch * 32 + j);
-                            ++n_pend;
-                        }
-                    }
-                    // pass 2 (rare after the first tiles): sorted insertion, one copy of the code
-#pragma unroll 1
-                    for (int p = 0; p < n_pend; ++p) {
-                        const vl_key_t key = pend[p * kTileRows];
-                        if ((int64_t)(uint32_t)key == row || !(key < top[kTopK - 1])) continue;
-                        top[kTopK - 1] = key;            // replace the worst, then let it sink to its place
-#pragma unroll
-                        for (int t = kTopK - 1; t > 0; --t) {
-                            const vl_key_t lo = top[t - 1], hi = top[t];
-                            const bool sw = hi < lo;
-                            top[t - 1] = sw ? hi : lo;
-                            top[t] = sw ? lo : hi;
-                        }
-                        if (top[kTopK - 1] != ~0ull) worst = vl_unord((uint32_t)(top[kTopK - 1] >> 32));
-                    }
+                    if (ch + 2 < kTileCands / 32) tc_load32(taddr + (ch + 2) * 32, v0);
+                    examine(v1, bias_tile + (ch + 1) * 32, c0 + (ch + 1) * 32);
+                    __syncwarp();
+                    tc_wait_ld();
                 }
+                if (lane == 0 && warp == 2) { VL_T1(5); if (a.stats) atomicAdd(a.stats + 6, 1ull); }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);  // 4 warps -> accumulator free again
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * group);  // 4 warps -> accumulator free again
             }
-            if (ok && row < a.row_hi) {
-                int32_t* out = a.out_ids + ((row - a.row_lo) * a.segments + seg) * kTopK;
-#pragma unroll
-                for (int j = 0; j < kTopK; ++j) out[j] = top[j] == ~0ull ? VL_MAXINT : (int32_t)(uint32_t)top[j];
+            if (ok) {      // the warp writes its rows' lists, one row (32 ids = 128 bytes) per step
+                __syncwarp();
+                const int64_t first_row = a.row_lo + rt * kTileRows + quarter * 32;
+#pragma unroll 1
+                for (int r = 0; r < 32 && first_row + r < a.row_hi; ++r) {
+                    const vl_key_t k = warp_lists[r * kTopK + lane];
+                    a.out_ids[(((first_row + r - a.row_lo) * a.segments + seg) * kLists + group) * kTopK + lane] =
+                        k == ~0ull ? VL_MAXINT : (int32_t)(uint32_t)k;
+                }
+                __syncwarp();
             }
         }
     }
@@ -378,6 +504,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 }  // namespace
+
+#ifdef VL_KNN_STATS
+static unsigned long long* g_knn_stats = nullptr;
+extern "C" void vl_knn_debug_stats(unsigned long long* device_counters) { g_knn_stats = device_counters; }
+#endif
 
 extern "C" int vl_knn_prepare(const float* vectors, int64_t n, int dim, uint16_t* bf16_out, int dim_pad, float* sqnorm_out,
                               void* stream)
@@ -439,13 +570,19 @@ extern "C" int vl_knn_tile(const uint16_t* rows_bf16, int64_t n, int dim_pad, co
     a.seg_len = seg_len > 0 ? seg_len : kTileCands;
     a.out_ids = out_ids;
     a.status = status;
+    a.stats = nullptr;
+#ifdef VL_KNN_STATS
+    a.stats = g_knn_stats;
+#endif
 
-    cudaError_t e = cudaFuncSetAttribute(knn_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    const bool resident = a.kblocks <= kResidentKBlocks;
+    auto kernel = resident ? knn_tile_kernel<true> : knn_tile_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     VL_CHECK_ARG(e == cudaSuccess, "vl_knn_tile: %s", cudaGetErrorString(e));
     const int64_t items = ((row_hi - row_lo + kTileRows - 1) / kTileRows) * segments;
     const int sms = vl_sm_count();
     const unsigned grid = (unsigned)(items < sms ? items : sms);
-    knn_tile_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, a);
+    kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, a);
     VL_CHECK_LAUNCH("knn_tile_kernel");
     return 0;
 }

@@ -23,7 +23,9 @@ from .constants import MAXFLOAT, MAXINT
 from .kernels import calculate_distances, metric_code, sort_pairs_
 from .log import nvtx_range
 
-TILE_K = 32            # VL_KNN_TILE_K: proposals per row and candidate segment
+TILE_K = 32            # VL_KNN_TILE_K: ids per list
+TILE_LISTS = 2         # VL_KNN_TILE_LISTS: lists per row and candidate segment (even tiles, odd tiles)
+PER_SEGMENT = TILE_K * TILE_LISTS
 BLOCK_K = 64           # the bf16 copy is padded to a multiple of this many columns
 
 
@@ -42,13 +44,14 @@ def prepare(vectors: Tensor, want_norms: bool) -> Tuple[Tensor, Optional[Tensor]
 
 def proposals(rows_bf16: Tensor, norms: Optional[Tensor], rows: Tuple[int, int], candidates: Tuple[int, int],
               segments: int) -> Tensor:
-    """int32 [rows, segments * 32]: per row the 32 best-scoring candidate ids of each of `segments`
-    equal parts of the candidate range (approximate scores; the row itself excluded), MAXINT-padded."""
+    """int32 [rows, segments * 64]: per row and per part of the candidate range (`segments` equal
+    parts) two lists of 32 ids, the best-scoring candidates of the part's even and of its odd
+    128-candidate tiles (approximate scores; the row itself excluded), MAXINT-padded."""
     _lib.require_cuda(rows_bf16, norms)
     assert rows_bf16.dtype == torch.bfloat16 and rows_bf16.is_contiguous()
     (n, dim_pad) = rows_bf16.size()
     (lo, hi) = rows
-    out = torch.empty((hi - lo, segments * TILE_K), dtype=torch.int32, device=rows_bf16.device)
+    out = torch.empty((hi - lo, segments * PER_SEGMENT), dtype=torch.int32, device=rows_bf16.device)
     check(lib().vl_knn_tile(ptr(rows_bf16), ctypes.c_int64(n), dim_pad, ptr(norms), ctypes.c_int64(lo), ctypes.c_int64(hi),
                             ctypes.c_int64(candidates[0]), ctypes.c_int64(candidates[1]), segments, ptr(out),
                             ptr(_lib.status_word(rows_bf16.device)), stream_of(rows_bf16)), "vl_knn_tile")
@@ -72,12 +75,12 @@ def exact_lists(vectors: Tensor, ids: Tensor, row_lo: int, width: int, metric: s
 
 def knn_start_graph(vectors: Tensor, width: int, config: Dict, group=None) -> Tuple[Tensor, Tensor]:
     """Start graph [N, width] (ids, exact distances) for generate_ann.  config["knn_segments"]
-    (default ceil(width / 32)) parts of the row range each contribute their 32 best proposals per
+    (default ceil(width / 64)) parts of the row range each contribute their 64 best proposals per
     row.  With `group`, each rank computes the lists of its share of the rows and the lists are
     all-gathered (every rank holds all vectors)."""
     (n, dim) = vectors.size()
     metric = config.get("metric", "cosine")
-    segments = int(config.get("knn_segments", 0)) or max(1, (width + TILE_K - 1) // TILE_K)
+    segments = int(config.get("knn_segments", 0)) or max(1, (width + PER_SEGMENT - 1) // PER_SEGMENT)
     world, rank = 1, 0
     if group is not None:
         import torch.distributed as dist
