@@ -144,7 +144,7 @@ int vl_connected_components(const int32_t* ids, const float* dist, int64_t n, in
  * |row|^2 in fp32 (sqnorm_out, may be NULL).
  *
  * vl_knn_tile: proposals for every row in [row_lo, row_hi).  The candidate range
- * [cand_lo, cand_hi) is cut into `segments` equal parts (each a multiple of 128 candidates, the
+ * [cand_lo, cand_hi) is cut into `segments` equal parts (each a multiple of 256 candidates, the
  * tile width), and within a part the tiles alternate between VL_KNN_TILE_LISTS = 2 lists: list 0
  * takes the part's tiles 0, 2, 4, ..., list 1 the tiles 1, 3, 5, ...  Each list holds the ids of
  * the VL_KNN_TILE_K candidates of its tiles with the smallest approximate score - bf16 inner

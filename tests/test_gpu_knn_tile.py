@@ -44,11 +44,11 @@ def test_prepare_rounds_to_bf16_pads_and_sums_squares(built_lib):
     np.testing.assert_allclose(n(norms), (v.astype(np.float64) ** 2).sum(1), rtol=1e-5)
 
 
-@pytest.mark.parametrize("count,segments,rows", [(1000, 1, (0, 1000)), (2500, 3, (300, 1700)), (130, 2, (0, 130))])
+@pytest.mark.parametrize("count,segments,rows", [(1000, 1, (0, 1000)), (2500, 3, (300, 1700)), (130, 2, (0, 130)), (700, 2, (5, 650))])
 def test_proposals_are_the_exact_top_of_every_list_on_integer_data(count, segments, rows, built_lib):
     """Integer-valued rows below 256 are exact in bf16 and their inner products are exact in the fp32
     accumulator, so every list must hold exactly the 32 nearest (squared L2, ties by id) of its
-    candidates - the even or the odd 128-candidate tiles of its segment - the row itself left out."""
+    candidates - the even or the odd 256-candidate tiles of its segment - the row itself left out."""
     from vectorlink_gpu.knn_tile import prepare, proposals
     rng = np.random.default_rng(count)
     v = sift_like(rng, count)
@@ -57,7 +57,7 @@ def test_proposals_are_the_exact_top_of_every_list_on_integer_data(count, segmen
     assert status_clear()
     assert got.shape == (rows[1] - rows[0], segments * 64)
     per_segment = (count + segments - 1) // segments
-    seg_len = (per_segment + 127) // 128 * 128                 # the kernel cuts the range at multiples of 128
+    seg_len = (per_segment + 255) // 256 * 256                 # the kernel cuts the range at multiples of its tile width
     d = ((v[rows[0]:rows[1], None, :].astype(np.float64) - v[None, :, :].astype(np.float64)) ** 2).sum(2)
     d[np.arange(rows[1] - rows[0]), np.arange(rows[0], rows[1])] = np.inf
     ids = np.arange(count)
@@ -65,7 +65,7 @@ def test_proposals_are_the_exact_top_of_every_list_on_integer_data(count, segmen
         lo, hi = s * seg_len, min(count, (s + 1) * seg_len)
         for parity in (0, 1):
             part = got[:, (2 * s + parity) * 32:(2 * s + parity + 1) * 32]
-            members = ids[(ids >= lo) & (ids < hi) & ((((ids - lo) // 128) & 1) == parity)]
+            members = ids[(ids >= lo) & (ids < hi) & ((((ids - lo) // 256) & 1) == parity)]
             if len(members) == 0:
                 assert (part == MAXINT).all()
                 continue

@@ -3,7 +3,7 @@
 // (vectorlink_gpu/utils.py:35-41, called at ann.py:116-118).  Not in the reference.
 //
 // The pass only PROPOSES candidates: bf16 inner products of a tile of 128 rows against tiles
-// of 128 candidate rows on the 5th-generation tensor cores, a per-row running top-k of the
+// of 256 candidate rows on the 5th-generation tensor cores, a per-row running top-k of the
 // approximate score (|c|^2 - 2<q,c> for squared L2, -2<q,c> for cosine).  The caller then
 // re-evaluates every proposed pair with the exact fp32 summation tree (vl_calculate_distances)
 // and orders them with vl_sort_pairs, so the lists that enter the graph carry the same exact
@@ -12,12 +12,14 @@
 // Shape of the kernel (one CTA per SM, persistent over work items = row tile x candidate segment):
 //   warp 0, one lane : TMA producer - cp.async.bulk.tensor 2D loads of 64-column k-blocks (128 B
 //                      rows, 128B swizzle) into a shared-memory ring, completion on an mbarrier
-//                      per stage.  Rows of at most 256 padded columns keep the row tile resident
-//                      (loaded once per work item) and stream only candidate tiles (4 stages of
-//                      16 KB); longer rows stream both operands (3 stages of 32 KB);
-//   warp 1, one lane : issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32, M=128, N=128, K=16)
+//                      per stage.  Rows of at most 128 padded columns keep the row tile resident
+//                      (loaded once per work item) and stream only candidate tiles (3 stages of
+//                      32 KB); longer rows stream both operands (3 stages of 48 KB);
+//   warp 1, one lane : issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32, M=128, N=256, K=16)
 //                      from shared-memory descriptors into one of two TMEM accumulators
-//                      (128 columns each), tcgen05.commit releases the stage / publishes the tile;
+//                      (256 columns each: all of TMEM), tcgen05.commit releases the stage /
+//                      publishes the tile.  (N=128 tiles measured 17 % slower: the row operand is
+//                      fetched from shared memory once per instruction whatever N is);
 //   warps 2..9       : two groups of four.  Group g owns accumulator g, i.e. every second candidate
 //                      tile of a segment, and keeps its own lists, so a row ends up with two lists
 //                      per segment (the best of the even tiles and the best of the odd tiles) and
@@ -42,18 +44,19 @@
 namespace {
 
 constexpr int kTileRows = 128;                 // M of the MMA: rows of the row tile
-constexpr int kTileCands = 128;                // N of the MMA: candidates per tile
+constexpr int kTileCands = 256;                // N of the MMA: candidates per tile
 constexpr int kBlockK = 64;                    // bf16 elements per k-block = one 128-byte swizzle row
-constexpr int kMaxStages = 4;                  // barrier slots; resident mode uses 4 stages, streaming mode 3
-constexpr int kResidentKBlocks = 4;            // row tiles of up to 4 k-blocks (256 columns) stay in shared memory
+constexpr int kMaxStages = 4;                  // barrier slots (3 stages in use)
+constexpr int kResidentKBlocks = 2;            // row tiles of up to 2 k-blocks (128 columns) stay in shared memory
 constexpr int kTopK = VL_KNN_TILE_K;           // keys per list
 constexpr int kLists = VL_KNN_TILE_LISTS;      // lists per row and segment: one per selection group
 constexpr int kThreads = 320;                  // warp 0 producer, warp 1 MMA, warps 2-9 selection (two groups of four)
-constexpr uint32_t kTileBytes = kTileRows * kBlockK * 2;              // 16 KB: one operand's k-block
-// operand region, 128 KB: resident mode = 4 candidate stages of 16 KB + the row tile's 4 k-blocks;
-// streaming mode = 3 stages of (candidates + rows) 32 KB
-constexpr uint32_t kOperandBytes = 8 * kTileBytes;
-constexpr uint32_t kOffRowTile = 4 * kTileBytes;
+constexpr uint32_t kTileBytes = kTileRows * kBlockK * 2;              // 16 KB: one k-block of the row tile
+constexpr uint32_t kCandBytes = kTileCands * kBlockK * 2;             // 32 KB: one k-block of a candidate tile
+// operand region, 144 KB: resident mode = 3 candidate stages of 32 KB + the row tile's 2 k-blocks;
+// streaming mode = 3 stages of (candidates 32 KB + rows 16 KB)
+constexpr uint32_t kOperandBytes = 3 * (kCandBytes + kTileBytes);
+constexpr uint32_t kOffRowTile = 3 * kCandBytes;
 constexpr uint32_t kTmemCols = 2 * kTileCands;                         // two accumulators
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;             // 2 s per wait
 
@@ -130,7 +133,7 @@ __device__ __forceinline__ void tc_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]^T, bf16 inputs, fp32 accumulate, M=128 N=128 K=16
+// D[tmem] (+)= A[smem] * B[smem]^T, bf16 inputs, fp32 accumulate, M=128 N=256 K=16
 __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -160,7 +163,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     return (uint64_t)((addr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N=128, M=128
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N=256, M=128
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileCands >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
 
 #ifdef VL_KNN_STATS
@@ -178,7 +181,7 @@ struct KnnArgs {
     int64_t row_lo, row_hi;   // rows that get lists
     int64_t cand_lo, cand_hi; // candidates offered to every row
     int segments;             // the candidate range is cut into this many parts, each with its own top-k
-    int64_t seg_len;          // candidates per part (a multiple of 128)
+    int64_t seg_len;          // candidates per part (a multiple of 256)
     int32_t* out_ids;         // [row_hi - row_lo, segments, kLists, kTopK]
     int* status;
     unsigned long long* stats; // cycle counters of a profiling build (-DVL_KNN_STATS), else unused
@@ -204,10 +207,10 @@ __device__ __forceinline__ uint32_t pick32(const uint32_t (&v)[32], int j)
 // tiles go through the ring; otherwise a ring stage holds one k-block of both operands.
 template <bool RESIDENT>
 __global__ void __launch_bounds__(kThreads, 1)
-knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
+knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_cand, const KnnArgs a)
 {
-    constexpr uint32_t kStages = RESIDENT ? 4 : 3;
-    constexpr uint32_t kStageBytes = RESIDENT ? kTileBytes : 2 * kTileBytes;
+    constexpr uint32_t kStages = 3;
+    constexpr uint32_t kStageBytes = RESIDENT ? kCandBytes : kCandBytes + kTileBytes;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -274,8 +277,8 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
                     { VL_T0(); ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status); VL_T1(0); }
                     if (!ok) break;
                     mbar_expect_tx(bar_full + 8 * s, kStageBytes);
-                    if (!RESIDENT) tma_load_2d(base + s * kStageBytes + kTileBytes, &tmap, kb * kBlockK, (int)row0, bar_full + 8 * s);
-                    tma_load_2d(base + s * kStageBytes, &tmap, kb * kBlockK, (int)c0, bar_full + 8 * s);
+                    if (!RESIDENT) tma_load_2d(base + s * kStageBytes + kCandBytes, &tmap, kb * kBlockK, (int)row0, bar_full + 8 * s);
+                    tma_load_2d(base + s * kStageBytes, &tmap_cand, kb * kBlockK, (int)c0, bar_full + 8 * s);
                 }
             }
         }
@@ -320,7 +323,7 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t a_desc = smem_desc_sw128(RESIDENT ? base + kOffRowTile + kb * kTileBytes
-                                                                     : base + s * kStageBytes + kTileBytes);
+                                                                     : base + s * kStageBytes + kCandBytes);
                     const uint64_t b_desc = smem_desc_sw128(base + s * kStageBytes);
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)      // 16 bf16 = 32 bytes = 2 descriptor units per step
@@ -409,14 +412,14 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
 
             // score offsets of a tile, four columns per lane: |c|^2 (squared L2) or 0 (cosine), +inf past the
             // segment's end so that such a column never qualifies
-            auto load_bias = [&](int64_t c0, float (&b)[4]) {
+            auto load_bias = [&](int64_t c0, float (&b)[kTileCands / 32]) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int q = 0; q < kTileCands / 32; ++q) {
                     const int64_t c = c0 + lane + 32 * q;
                     b[q] = (c < c_end) ? (a.bias ? __ldg(a.bias + c) : 0.0f) : kInf;
                 }
             };
-            float next_bias[4];
+            float next_bias[kTileCands / 32];
             const int64_t c_first = c_begin + (int64_t)group * kTileCands;
             if (c_first < c_end) load_bias(c_first, next_bias);
 #pragma unroll 1
@@ -425,7 +428,7 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const KnnArgs a)
                 // next tile's offsets are requested now and stored when this tile is done
                 __syncwarp();
 #pragma unroll
-                for (int q = 0; q < 4; ++q) bias_tile[lane + 32 * q] = next_bias[q];
+                for (int q = 0; q < kTileCands / 32; ++q) bias_tile[lane + 32 * q] = next_bias[q];
                 __syncwarp();
                 if (c0 + 2 * kTileCands < c_end) load_bias(c0 + 2 * kTileCands, next_bias);
                 const uint32_t tph = used & 1u;
@@ -556,6 +559,12 @@ extern "C" int vl_knn_tile(const uint16_t* rows_bf16, int64_t n, int dim_pad, co
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     VL_CHECK_ARG(cr == CUDA_SUCCESS, "vl_knn_tile: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    CUtensorMap tmap_cand;
+    const cuuint32_t box_cand[2] = {(cuuint32_t)kBlockK, (cuuint32_t)kTileCands};
+    cr = encode(&tmap_cand, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(rows_bf16), gdim, gstride, box_cand, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    VL_CHECK_ARG(cr == CUDA_SUCCESS, "vl_knn_tile: cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
     KnnArgs a;
     a.bias = sqnorm;
@@ -582,7 +591,7 @@ extern "C" int vl_knn_tile(const uint16_t* rows_bf16, int64_t n, int dim_pad, co
     const int64_t items = ((row_hi - row_lo + kTileRows - 1) / kTileRows) * segments;
     const int sms = vl_sm_count();
     const unsigned grid = (unsigned)(items < sms ? items : sms);
-    kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, a);
+    kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, tmap_cand, a);
     VL_CHECK_LAUNCH("knn_tile_kernel");
     return 0;
 }
