@@ -94,25 +94,29 @@ def make_data(w, n, device, seed=0, queries=None):
     return vectors.contiguous(), q.contiguous()
 
 
-def brute_force_topk(vectors, queries, k, metric):
+def brute_force_topk(vectors, queries, k, metric, query_chunk=8192):
     """Exact top-k on the GPU in fp32 (ground truth for recall; measurement harness only)."""
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.set_float32_matmul_precision("highest")
-    best_d = torch.full((queries.size(0), k), float("inf"), device=vectors.device)
-    best_i = torch.zeros((queries.size(0), k), dtype=torch.int64, device=vectors.device)
-    qn = (queries * queries).sum(1, keepdim=True)
-    for lo in range(0, vectors.size(0), 262_144):
-        blk = vectors[lo:lo + 262_144]
-        dots = queries @ blk.t()
-        d = (qn - 2 * dots + (blk * blk).sum(1).unsqueeze(0)) if metric == "l2" else (1 - dots) / 2
-        cd, ci = torch.topk(d, min(k, blk.size(0)), dim=1, largest=False)
-        alld = torch.cat([best_d, cd], 1)
-        alli = torch.cat([best_i, ci + lo], 1)
-        best_d, sel = torch.topk(alld, k, dim=1, largest=False)
-        best_i = torch.gather(alli, 1, sel)
+    out = []
+    for q0 in range(0, queries.size(0), query_chunk):
+        qs = queries[q0:q0 + query_chunk]
+        best_d = torch.full((qs.size(0), k), float("inf"), device=vectors.device)
+        best_i = torch.zeros((qs.size(0), k), dtype=torch.int64, device=vectors.device)
+        qn = (qs * qs).sum(1, keepdim=True)
+        for lo in range(0, vectors.size(0), 262_144):
+            blk = vectors[lo:lo + 262_144]
+            dots = qs @ blk.t()
+            d = (qn - 2 * dots + (blk * blk).sum(1).unsqueeze(0)) if metric == "l2" else (1 - dots) / 2
+            cd, ci = torch.topk(d, min(k, blk.size(0)), dim=1, largest=False)
+            alld = torch.cat([best_d, cd], 1)
+            alli = torch.cat([best_i, ci + lo], 1)
+            best_d, sel = torch.topk(alld, k, dim=1, largest=False)
+            best_i = torch.gather(alli, 1, sel)
+        out.append(best_i)
     torch.backends.cuda.matmul.allow_tf32 = prev
-    return best_i
+    return torch.cat(out, 0) if out else torch.zeros((0, k), dtype=torch.int64, device=vectors.device)
 
 
 def recall_at_k(found_ids, truth, k):

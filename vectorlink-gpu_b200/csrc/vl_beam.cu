@@ -506,24 +506,42 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
             // offering it again can neither add nor move anything.
             bool changed = false;
             vl_key_t cut = sq[sq_len - 1];
+            // First gather the few candidates that can enter at all (below the queue's current last key,
+            // not the row itself, not excluded) to the front of `todo`, then merge them 32 at a time:
+            // usually one merge per iteration instead of one per 32-candidate chunk that holds an entrant.
+            // "The L best of a union" does not depend on the grouping, so the queue is the same.
+            int n_in = 0;
 #pragma unroll 1
             for (int t0 = 0; t0 < n_todo; t0 += 32) {
                 const int t = t0 + lane;
-                vl_key_t key = t < n_todo ? candk[todo[t]] : kSent;
+                const unsigned short ci = t < n_todo ? todo[t] : (unsigned short)0;
+                const vl_key_t key = t < n_todo ? candk[ci] : kSent;
                 bool want = key < cut;
-                if (!__any_sync(0xffffffffu, want)) continue;
-                if (want) {
-                    int32_t id = vl_key_id(key);
-                    if (id == self_id) want = false;
-                    else if (excl) {
+                if (__any_sync(0xffffffffu, want)) {
+                    if (want) {
+                        int32_t id = vl_key_id(key);
+                        if (id == self_id) want = false;
+                        else if (excl) {
 #pragma unroll 1
-                        for (int x = 0; x < p.exclude_w; ++x) {   // kernels.py:478-488
-                            int32_t ex = excl[x];
-                            if (ex == VL_MAXINT) break;
-                            if (ex == id) { want = false; break; }
+                            for (int x = 0; x < p.exclude_w; ++x) {   // kernels.py:478-488
+                                int32_t ex = excl[x];
+                                if (ex == VL_MAXINT) break;
+                                if (ex == id) { want = false; break; }
+                            }
                         }
                     }
+                    const unsigned mask = __ballot_sync(0xffffffffu, want);
+                    __syncwarp();                                     // every lane has read its todo[t] of this chunk
+                    if (want) todo[n_in + __popc(mask & ((1u << lane) - 1u))] = ci;   // n_in <= t0: never ahead of the reads
+                    n_in += __popc(mask);
                 }
+            }
+            __syncwarp();
+#pragma unroll 1
+            for (int t0 = 0; t0 < n_in; t0 += 32) {
+                const int t = t0 + lane;
+                const vl_key_t key = t < n_in ? candk[todo[t]] : kSent;
+                const bool want = key < cut;
                 if (!__any_sync(0xffffffffu, want)) continue;
                 changed |= merge_chunk(sq, sq_n, sq_len, key, want, lane, mpos);
                 st_sm += 1;
