@@ -306,10 +306,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--loops", type=int, default=0, help="override optimization_loops")
     ap.add_argument("--quick", action="store_true", help="skip the host-buffer pass and the recall evaluation")
+    ap.add_argument("--no-tile-start", action="store_true", help="skip the extra builds with the tensor-core start graph")
     ap.add_argument("--skip-e2e", action="store_true", help="skip only the host-buffer pass (long single builds)")
     ap.add_argument("--init", default="circulant", choices=["circulant", "knn_tile"],
                     help="start graph of the build: the reference's circulant graph (default) or the tensor-core tile pass")
     ap.add_argument("--mode", default="rows", choices=["rows", "shards"], help="multi-GPU build mode (see sharded.py)")
+    ap.add_argument("--merge", default="tile", choices=["tile", "search"], help="how mode shards finds cross-shard neighbours")
     args = ap.parse_args()
     name = args.workload
     w = dict(WORKLOADS[name])
@@ -341,6 +343,10 @@ def main():
         kw["optimization_loops"] = args.loops
     if args.init != "circulant":
         kw["init"] = args.init
+        if not args.loops:
+            # the lists of the tile pass are already near neighbours: one round (search + prune) ends in the same
+            # graph as three (measured on config 2), so that is how this start graph is meant to be used
+            kw["optimization_loops"] = 1
     # strong scaling: the job is always the workload's w["n"] vectors; rank r starts with rows
     # [lo_r, hi_r) of them in its HBM.  A step all-gathers the shards and runs the build with every
     # round's rows split across the ranks (ShardedANN mode "rows"): the graph is bit-identical to
@@ -367,7 +373,7 @@ def main():
 
     def build(v):
         if world > 1:
-            return ShardedANN(v, group=dist.group.WORLD, mode=args.mode, **kw)
+            return ShardedANN(v, group=dist.group.WORLD, mode=args.mode, merge=args.merge, **kw)
         return ANN(vectors=v, **kw)
 
     def step_device():
@@ -448,6 +454,36 @@ def main():
         gsample = min(index.vectors.size(0), 10_000)
         gtruth = brute_force_topk(index.vectors, index.vectors[:gsample], 11, w["metric"])[:, 1:]
         graph_recall = recall_at_k(index.beams[:gsample], gtruth, 10)
+
+    # the opt-in tensor-core start graph, beside the headline (which is the reference's algorithm): same
+    # data, same queries, one round
+    tile_start = None
+    if not args.quick and args.init == "circulant" and not args.no_tile_start:
+        kw_tile = dict(kw, init="knn_tile", optimization_loops=1)
+
+        def build_tile():
+            if world > 1:
+                return ShardedANN(vectors, group=dist.group.WORLD, mode=args.mode, merge=args.merge, **kw_tile)
+            return ANN(vectors=vectors, **kw_tile)
+
+        ann = None                      # frees the first index before the second is built
+        alt = build_tile()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            alt = build_tile()
+        t1.record()
+        barrier()
+        alt_ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(alt_ms, op=dist.ReduceOp.MAX)
+        alt_index = alt.index if world > 1 else alt
+        alt_found = alt.search(queries)[0] if world > 1 else alt.search(queries).indices
+        tile_start = {"init": "knn_tile", "optimization_loops": 1, "ms_per_step": float(alt_ms.item()),
+                      "value": total / (float(alt_ms.item()) * 1e-3), "unit": "vectors/s",
+                      "graph_recall_at_10": recall_at_k(alt_index.beams[:gsample], gtruth, 10),
+                      "search_recall_at_10": recall_at_k(alt_found, truth, 10)}
     status = _lib.read_status(dev)
 
     times = torch.tensor([ms_total, e2e_ms, search_ms], device=dev, dtype=torch.float64)
@@ -474,14 +510,15 @@ def main():
                                     ("vectors all-gathered; each round's rows split evenly across ranks, searched and pruned "
                                      "by their rank, lists all-gathered (NCCL): the single-GPU graph") if args.mode == "rows" else
                                     ("each rank builds the graph of its own shard, then a merge pass: rows all-gathered "
-                                     "chunk by chunk, every shard searched for the foreign rows, candidate lists "
-                                     "all-gathered and merged by the owner (NCCL)"))},
+                                     "chunk by chunk, every shard scanned for the foreign rows (%s), candidate lists "
+                                     "all-gathered and merged by the owner (NCCL)" % args.merge))},
             "e2e": {"value": (total / (e2e_ms / args.steps * 1e-3)) if e2e_ms == e2e_ms else None, "unit": "vectors/s",
                     "h2d_bytes_per_step": total * dim * 4, "d2h_bytes_per_step": total * kw["beam_size"] * 8},
             "gpu_launches": launches,
             "search": {"qps": queries.size(0) / (search_ms * 1e-3), "queries": queries.size(0), "k": 10,
                        "recall_at_10": recall, "ms": search_ms},
             "graph_recall_at_10": graph_recall,
+            "tile_start": tile_start,
             "roofline": roofline_of(build_classes, search_classes, peak, peak_kind, name, dim, kernel_share),
             "clocks": clocks, "status_word": status,
         }

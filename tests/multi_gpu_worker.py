@@ -12,6 +12,11 @@ import torch
 import torch.distributed as dist
 
 
+def _lib_status_clear(dev):
+    from vectorlink_gpu import _lib
+    return _lib.read_status(dev) == 0
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -57,21 +62,34 @@ def main():
         assert np.array_equal(tiny.index.beams.cpu().numpy(), wb), f"batch_size {batch}: graph differs from the oracle"
         assert np.array_equal(tiny.index.distances.cpu().numpy(), wd)
 
-    # mode "shards": local graphs + cross-shard merge; quality check against brute force
-    shards = ShardedANN(vectors[lo:hi].contiguous(), mode="shards", **kw)
-    ids2, _ = shards.search(queries)
+    # mode "shards": local graphs + cross-shard merge; quality check against brute force.  The merge finds a
+    # foreign row's neighbours in a shard either with the tensor-core tile pass (default) or by searching the
+    # shard's graph.
     full = vectors
     d = (1 - queries @ full.t()) / 2
     truth = torch.topk(d, 10, dim=1, largest=False).indices
-    hits = (ids2[:, :10].long().unsqueeze(2) == truth.unsqueeze(1)).any(2).float().mean().item()
-    assert hits >= 0.95, hits
-    b = shards.beams
-    assert b.shape == (hi - lo, kw["beam_size"]) and int(b[b != 2147483647].max()) < vectors.size(0)
     own = torch.arange(lo, hi, device=dev, dtype=torch.int32).unsqueeze(1)
-    assert bool((b != own).all()), "self loop in the merged graph"
+    dg = (1 - full[lo:hi] @ full.t()) / 2
+    dg[torch.arange(hi - lo, device=dev), torch.arange(lo, hi, device=dev)] = float("inf")
+    gtruth = torch.topk(dg, 10, dim=1, largest=False).indices
+    report = {}
+    for merge in ("tile", "search"):
+        shards = ShardedANN(vectors[lo:hi].contiguous(), mode="shards", merge=merge, **kw)
+        ids2, _ = shards.search(queries)
+        hits = (ids2[:, :10].long().unsqueeze(2) == truth.unsqueeze(1)).any(2).float().mean().item()
+        assert hits >= 0.95, (merge, hits)
+        b = shards.beams
+        assert b.shape == (hi - lo, kw["beam_size"]) and int(b[b != 2147483647].max()) < vectors.size(0)
+        assert bool((b != own).all()), "self loop in the merged graph"
+        graph_hits = (b[:, :10].long().unsqueeze(2) == gtruth.unsqueeze(1)).any(2).float().mean().item()
+        foreign = ((b < lo) | (b >= hi)) & (b != 2147483647)
+        assert bool(foreign.any()), "the merge pass brought no neighbour from the other shard"
+        report[merge] = (hits, graph_hits)
+    assert report["tile"][1] >= 0.9, report           # merged graph recall@10 against the exact neighbours
+    assert _lib_status_clear(dev)
     dist.barrier()
     if rank == 0:
-        print(f"MULTI_GPU_OK recall_shards={hits:.3f}")
+        print(f"MULTI_GPU_OK shards(search recall, graph recall) = {report}")
     dist.destroy_process_group()
 
 

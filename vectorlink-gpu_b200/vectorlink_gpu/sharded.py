@@ -9,12 +9,17 @@ Two build modes:
 mode="shards"
         1. every rank builds the graph of its own shard with the single-GPU path (no
            communication);
-        2. merge pass, chunk by chunk: the owners' rows are all-gathered, every rank searches
-           its local graph for the rows of the other shards (`ANN.search` on the local
-           index), the per-shard candidate lists [chunk, D] (global ids, distances) are
-           all-gathered, and each owner keeps the D best distinct (distance, id) pairs of its
-           own list and the G-1 foreign ones.  Work per GPU grows with the number of shards
-           (every shard is searched for every foreign row).
+        2. merge pass, chunk by chunk: the owners' rows are all-gathered, every rank looks
+           for the neighbours of the other shards' rows inside its own shard, the per-shard
+           candidate lists [chunk, D] (global ids, distances) are all-gathered, and each owner
+           keeps the D best distinct (distance, id) pairs of its own list and the G-1 foreign
+           ones.  How a rank finds a foreign row's neighbours in its shard: merge="tile"
+           (default) scores the foreign rows against the whole shard on the tensor cores
+           (the tile pass of knn_tile.py) and reranks the proposals with exact distances;
+           merge="search" beam-searches the shard's graph (`ANN.search` on the local index),
+           which only finds them when a seed lands in the right region of the shard.  Work
+           per GPU grows with the number of shards (every shard is scanned for every foreign
+           row).
 mode="rows" (default)
         the shards' vectors are all-gathered first (20M x 1024 fp32 is 82 GB of a B200's
         180 GB), then the single-GPU algorithm runs with the ROWS of every round split across
@@ -132,11 +137,13 @@ class ShardedANN:
     (with `replicate=True`) `.index`, an `ANN` over the whole set on every rank for `.search`.
     """
 
-    def __init__(self, local_vectors: Tensor, group=None, mode: str = "rows", merge: bool = True,
+    def __init__(self, local_vectors: Tensor, group=None, mode: str = "rows", merge=True,
                  replicate: bool = True, chunk_rows: int = 65536, **ann_kwargs):
         from .ann import ANN
         from .kernels import sort_pairs_
         assert mode in ("rows", "shards")
+        assert merge in (True, False, "tile", "search")
+        merge = "tile" if merge is True else merge
         self.group = group if group is not None else dist.group.WORLD
         group = self.group
         self.world = dist.get_world_size(group)
@@ -160,13 +167,42 @@ class ShardedANN:
             got = q.indices[:, :degree]
             return torch.where(got == MAXINT, got, got + base), q.distances[:, :degree]
 
+        tile_state = {}
+
+        def tile_fn(rows: Tensor):
+            """Neighbours of foreign rows inside this shard: tensor-core proposals over the whole shard,
+            exact distances, queue order (knn_tile.py).  The shard's bf16 copy is made once; the foreign
+            chunk is appended behind it so that one matrix holds both sides of the tile pass."""
+            from . import knn_tile
+            from .kernels import calculate_distances, metric_code
+            local = self.local.vectors
+            metric = self.local.configuration.get("metric", "cosine")
+            n_loc = local.size(0)
+            if not tile_state:
+                head, norms = knn_tile.prepare(local, want_norms=metric_code(metric) == 1)
+                both = torch.empty((n_loc + chunk_rows, head.size(1)), dtype=head.dtype, device=head.device)
+                both[:n_loc] = head
+                tile_state["both"] = both
+                if norms is not None:
+                    tile_state["norms"] = torch.cat([norms, torch.zeros(chunk_rows, dtype=norms.dtype, device=norms.device)])
+            both = tile_state["both"]
+            b = rows.size(0)
+            tail, _ = knn_tile.prepare(rows.contiguous(), want_norms=False)
+            both[n_loc:n_loc + b] = tail
+            got = knn_tile.proposals(both, tile_state.get("norms"), (n_loc, n_loc + b), (0, n_loc), 1)
+            d = calculate_distances(local, got, metric=metric, queries=rows.contiguous())
+            sort_pairs_(got, d, dedup=True)
+            got, d = got[:, :degree], d[:, :degree]
+            return torch.where(got == MAXINT, got, got + base), d
+
         def merge_fn(cand_ids: Tensor, cand_dist: Tensor, keep: int):
             sort_pairs_(cand_ids, cand_dist, dedup=True)      # (distance, id) order, repeats out
             return cand_ids[:, :keep], cand_dist[:, :keep]
 
         if merge and self.world > 1:
             ids, dist_ = merge_pass(self.local.vectors, ids.contiguous(), dist_.contiguous(), self.offsets, degree,
-                                    search_fn, merge_fn, chunk_rows, group)
+                                    tile_fn if merge == "tile" else search_fn, merge_fn, chunk_rows, group)
+            tile_state.clear()
         self.beams, self.distances = ids, dist_
         self.index = None
         if replicate:
