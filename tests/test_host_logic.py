@@ -80,3 +80,44 @@ def test_runner_flags_and_defaults_are_the_reference_runners():
     params = runner.build_params(args)
     assert params["vector_count"] == 500 and params["prune"] is True and params["parallel_visit_count"] == 4
     assert params["recall_search_queue_factor"] == 2 and params["optimization_loops"] == 1
+
+
+def test_bench_groups_launches_by_phase_and_keeps_the_fraction_honest():
+    """bench.launch_classes / roofline_of on fake launch records: the headline fraction is the
+    gathered bytes of the later build rounds, never the schedule's bytes."""
+    import torch
+    import bench
+
+    class Ev:
+        def __init__(self, t):
+            self.t = t
+
+        def elapsed_time(self, other):
+            return other.t - self.t
+
+    def rec(tag, t0, t1, evals, gathered, memo):
+        st = torch.zeros(24, dtype=torch.int64)
+        st[1] = gathered
+        return {"start": Ev(t0), "end": Ev(t1), "rows": 1000, "graph_w": 96, "iterations": 81, "evals": evals,
+                "memo": memo, "stats": st, "tag": tag}
+
+    prof = [rec("round0", 0, 1000, 10**9, 10**9, False), rec("self_recall", 1000, 1001, 10**5, 3 * 10**4, True),
+            rec("round1", 1001, 1501, 10**9, 2 * 10**8, True), rec("round2", 1501, 1901, 10**9, 10**8, True)]
+    cls = bench.launch_classes(prof, 1, 128)
+    assert set(cls) == {"build_round0", "self_recall", "build_later_rounds"}
+    later = cls["build_later_rounds"]
+    assert later["launches_per_step"] == 2 and later["ms_per_launch"] == 450
+    assert abs(later["gathered_fraction"] - 0.15) < 1e-12
+    roof = bench.roofline_of(cls, {}, 6534.5, "test", "none", 128, 0.99)
+    assert roof["class"] == "build_later_rounds" and roof["rows_served_from"] == "DRAM"
+    assert abs(roof["achieved"] - 3e8 * 524 / 0.9 / 1e9) < 1e-6
+    assert roof["frac"] < 1.0 and roof["classes"]["build_later_rounds"]["vs_reference_schedule"] > roof["frac"]
+    assert roof["traffic"] is None          # no capture on record for this workload name
+
+
+def test_tile_pass_wrappers_refuse_cpu_tensors(built_lib):
+    import torch
+    from vectorlink_gpu import _lib, knn_tile
+    import pytest as _pytest
+    with _pytest.raises(_lib.VlError):
+        knn_tile.prepare(torch.zeros(4, 64), want_norms=True)
