@@ -135,3 +135,41 @@ def test_build_from_the_tile_pass_beats_the_circulant_start(built_lib):
     r_plain, r_tiled = recall(plain), recall(tiled)
     assert r_tiled > r_plain and r_tiled >= 0.9, (r_plain, r_tiled)
     assert np.array_equal(oracle.calculate_distances(v, n(tiled.beams)), n(tiled.distances))
+
+
+def test_search_from_tensor_core_entry_points_vs_oracle_and_recall(built_lib):
+    """`search_entry_sample`: the entry points come from the tile pass, everything after that is the
+    reference's search - bit for bit the oracle's queue when it starts from the same seeds - and on
+    clustered rows the queries now reach their cluster, which the circulant seeds rarely do."""
+    from vectorlink_gpu import ANN
+    from vectorlink_gpu.ann import query_distances
+    rng = np.random.default_rng(12)
+    count, dim = 12000, 64
+    c = rng.standard_normal((300, dim)) * 3
+    v = (c[rng.integers(0, 300, count)] + 0.3 * rng.standard_normal((count, dim))).astype(np.float32)
+    v = (v / np.linalg.norm(v, axis=1, keepdims=True)).astype(np.float32)
+    q = (c[rng.integers(0, 300, 200)] + 0.3 * rng.standard_normal((200, dim))).astype(np.float32)
+    q = (q / np.linalg.norm(q, axis=1, keepdims=True)).astype(np.float32)
+    kw = dict(beam_size=16, visit_queue_factor=2, recall_search_queue_factor=2)
+    kn = oracle.bruteforce_knn(v, v, 16, exclude_self=True)
+    kd = oracle.calculate_distances(v, kn)
+    plain = ANN(t(v), beams=t(kn), distances=t(kd), **kw)
+    tiled = ANN(t(v), beams=t(kn), distances=t(kd), search_entry_sample=4096, **kw)
+    sq = tiled.search(t(q))
+    assert status_clear()
+    seeds = tiled._entry_seeds(t(q))
+    assert tuple(seeds.shape) == (200, 64) and int(seeds.max()) < count
+    sd = query_distances(t(q), t(v), seeds)
+    cfg = oracle.make_config(**kw)
+    oq = oracle.Queue(200, sq.length, sq.indices.size(1))
+    oq.insert(n(seeds), n(sd))
+    oracle.closest_vectors(q, oq, v, kn, cfg)
+    assert np.array_equal(n(sq.indices), oq.indices) and np.array_equal(n(sq.distances), oq.distances)
+    truth = oracle.bruteforce_knn(v, q, 10)
+
+    def recall(queue):
+        got = n(queue.indices[:, :10])
+        return np.mean([len(set(got[i]) & set(truth[i])) / 10 for i in range(200)])
+
+    r_plain, r_tiled = recall(plain.search(t(q))), recall(sq)
+    assert r_tiled >= 0.95 and r_tiled > r_plain + 0.2, (r_plain, r_tiled)

@@ -617,7 +617,8 @@ class ANN:
     reference), prune_mode ("first" = the reference's detour test against y's first neighbour only,
     "full" = against all of them), symmetrize (add reverse edges after the build; off = the reference),
     init ("circulant" = the reference's start graph; "knn_tile" = exact-reranked proposals of a tensor-core
-    tile pass, see knn_tile.py) and group (a torch.distributed group whose ranks all pass the same vectors: the
+    tile pass, see knn_tile.py), search_entry_sample (0 = the reference's circulant seeds; S > 0: `.search` starts
+    every query from its best 64 of S evenly spaced rows, scored on the tensor cores, see `_entry_seeds`) and group (a torch.distributed group whose ranks all pass the same vectors: the
     build's rows are split across them, see generate_ann)."""
 
     def __init__(self, vectors: Tensor, prune: bool = True, beam_size: int = 24, parallel_visit_count: int = 4,
@@ -625,7 +626,7 @@ class ANN:
                  optimization_loops: int = 3, batch_size: int = 10_000, recall_search_queue_factor: int = 3,
                  speculative_readahead: int = 5, beams: Optional[Tensor] = None, distances: Optional[Tensor] = None,
                  metric: str = "cosine", search_seed_factor: int = 1, group=None, symmetrize: bool = False,
-                 prune_mode: str = "first", init: str = "circulant"):
+                 prune_mode: str = "first", init: str = "circulant", search_entry_sample: int = 0):
         (count, dim) = vectors.size()
         assert vectors.dtype == torch.float32
         _lib.require_cuda(vectors)
@@ -652,6 +653,9 @@ class ANN:
         assert init in ("circulant", "knn_tile")
         if init != "circulant":
             self.configuration["init"] = init
+        if search_entry_sample:
+            self.configuration["search_entry_sample"] = int(search_entry_sample)
+        self._entry = None
         self.vectors = vectors.contiguous()
         wall_start = time.time()
         if beams is not None:
@@ -755,18 +759,36 @@ class ANN:
         extra_capacity = max(queue_size, config["parallel_visit_count"] * config["beam_size"])
         seed_count = queue_size * max(1, int(config.get("search_seed_factor", 1)))
         beams = self.beams.contiguous()
-        if (seed_count > extra_capacity and query.size(0) > 0 and not config.get("stepwise", False)
-                and _fused_shape_ok(self.vectors, beams.size(1), queue_size, queue_size + extra_capacity, config)):
-            # widened seed scan: the fused kernel starts every row from an empty queue and merges the
+        entry_sample = int(config.get("search_entry_sample", 0))
+        fused_ok = (query.size(0) > 0 and not config.get("stepwise", False)
+                    and _fused_shape_ok(self.vectors, beams.size(1), queue_size, queue_size + extra_capacity, config))
+        if entry_sample > 0 and query.size(0) > 0:
+            # entry points from the tensor-core pass instead of circulant seeds
+            seeds = self._entry_seeds(query)
+            d = query_distances(query, self.vectors, seeds, _metric_of(config))
+
+            def seeded_queue():
+                q = Queue(query.size(0), queue_size, queue_size + extra_capacity, device=self.vectors.device)
+                q.insert(seeds[:, :extra_capacity].contiguous(), d[:, :extra_capacity].contiguous())
+                return q
+
+            if not fused_ok:
+                search_queue = seeded_queue()
+                closest_vectors(query, search_queue, self.vectors, beams, config, None)
+                return search_queue
+            seed_count = seeds.size(1)
+        if (entry_sample > 0 or seed_count > extra_capacity) and fused_ok:
+            # many seeds: the fused kernel starts every row from an empty queue and merges the
             # seeds itself, so the best-Q selection needs no separate sort
             _lib.require_cuda(query, self.vectors, beams)
             dev = self.vectors.device
-            seeds = generate_queue_circulants(query.size(0), self.vectors.size(0), primes(seed_count, dev), first_row)
-            d = query_distances(query, self.vectors, seeds, _metric_of(config))
+            if entry_sample <= 0:
+                seeds = generate_queue_circulants(query.size(0), self.vectors.size(0), primes(seed_count, dev), first_row)
+                d = query_distances(query, self.vectors, seeds, _metric_of(config))
             queue = Queue(query.size(0), queue_size, queue_size + extra_capacity, device=dev)
 
             def stepwise(lo, hi):
-                q = initial_search_queue(self.vectors, query, config, first_row)
+                q = seeded_queue() if entry_sample > 0 else initial_search_queue(self.vectors, query, config, first_row)
                 n = closest_vectors_stepwise(query, q, self.vectors, beams, config, None)
                 queue.indices.copy_(q.indices)
                 queue.distances.copy_(q.distances)
@@ -780,6 +802,30 @@ class ANN:
         search_queue = initial_search_queue(self.vectors, query, config, first_row)
         closest_vectors(query, search_queue, self.vectors, beams, config, None)
         return search_queue
+
+    def _entry_seeds(self, query: Tensor) -> Tensor:
+        """int32 [B, 64]: for every query the 64 best-scoring of S = config["search_entry_sample"] evenly
+        spaced rows of the index (bf16 inner products on the tensor cores, knn_tile.py), as global ids,
+        MAXINT-padded.  Added: the reference seeds a search with Q rows at fixed offsets from the query's
+        batch position (utils.py:26-32), which finds the query's neighbourhood only if one of them happens
+        to lie near it; on clustered data most queries then never reach their cluster.  The seeds only pick
+        where the search starts: their distances are taken exactly afterwards, like any other seed's."""
+        from . import knn_tile
+        (n, _) = self.vectors.size()
+        sample = min(n, int(self.configuration["search_entry_sample"]))
+        metric = _metric_of(self.configuration)
+        if self._entry is None or self._entry["sample"] != sample:
+            ids = (torch.arange(sample, device=self.vectors.device, dtype=torch.int64) * n // sample).to(torch.int32)
+            rows_bf16, norms = knn_tile.prepare(self.vectors[ids.long()].contiguous(), want_norms=metric_code(metric) == 1)
+            self._entry = {"sample": sample, "ids": ids, "rows": rows_bf16, "norms": norms}
+        e = self._entry
+        b = query.size(0)
+        tail, _ = knn_tile.prepare(query, want_norms=False)
+        both = torch.cat([e["rows"], tail], 0)
+        norms = None if e["norms"] is None else torch.cat([e["norms"], torch.zeros(b, dtype=torch.float32, device=query.device)])
+        picks = knn_tile.proposals(both, norms, (sample, sample + b), (0, sample), 1)      # indices into the sample
+        valid = picks != MAXINT
+        return torch.where(valid, e["ids"][picks.clamp(max=sample - 1).long()], picks).contiguous()
 
     def dump_logs(self) -> Dict:
         """ann.py:479-489."""
