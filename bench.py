@@ -410,6 +410,7 @@ def main():
     ev1.record()
     barrier()
     launches = _lib.LAUNCHES - launches0
+    loops_run = vl_ann.generate_ann.last_loops
     profile = vl_ann.PROFILE
     vl_ann.PROFILE = None
     ms_total = ev0.elapsed_time(ev1)
@@ -529,7 +530,7 @@ def main():
             "metric": "graph_build_vectors_per_s", "value": total / (ms_per_step * 1e-3), "unit": "vectors/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": name, "vectors": total, "vectors_per_gpu": n, "dim": dim, **kw, "loops_run": vl_ann.generate_ann.last_loops,
+            "config": {"workload": name, "vectors": total, "vectors_per_gpu": n, "dim": dim, **kw, "loops_run": loops_run,
                        "l2_policy": "inputs (vectors %d MB + graph) exceed the 126 MB L2" % (total * dim * 4 // 2**20),
                        "sharding": ("none" if world == 1 else
                                     ("vectors all-gathered; each round's rows split evenly across ranks, searched and pruned "

@@ -233,7 +233,7 @@ def symmetrize(vectors: Tensor, beams: Tensor, distances: Tensor, keep: Optional
     node up to `keep` (default half its degree) of its reverse edges.  The new row is the
     distinct ids of: the best degree-keep forward neighbours, then the reverse neighbours, then
     the remaining forward ones - cut to the degree and ordered by distance.  Not in the
-    reference's live code, so there is no parity target; it is judged by recall."""
+    reference's live code, so there is no parity target; it is assessed by recall."""
     (n, d) = beams.size()
     keep = max(1, d // 2) if keep is None else min(keep, d)
     rev = reverse_edges(beams, scan=d, keep=keep)
