@@ -814,16 +814,20 @@ class ANN:
         (n, _) = self.vectors.size()
         sample = min(n, int(self.configuration["search_entry_sample"]))
         metric = _metric_of(self.configuration)
-        if self._entry is None or self._entry["sample"] != sample:
+        b = query.size(0)
+        if self._entry is None or self._entry["sample"] != sample or self._entry["both"].size(0) < sample + b:
             ids = (torch.arange(sample, device=self.vectors.device, dtype=torch.int64) * n // sample).to(torch.int32)
             rows_bf16, norms = knn_tile.prepare(self.vectors[ids.long()].contiguous(), want_norms=metric_code(metric) == 1)
-            self._entry = {"sample": sample, "ids": ids, "rows": rows_bf16, "norms": norms}
+            # one matrix for both sides of the tile pass: the sample's rows, then room for a batch of queries
+            room = max(b, 16_384)
+            both = torch.zeros((sample + room, rows_bf16.size(1)), dtype=rows_bf16.dtype, device=rows_bf16.device)
+            both[:sample] = rows_bf16
+            if norms is not None:
+                norms = torch.cat([norms, torch.zeros(room, dtype=torch.float32, device=norms.device)])
+            self._entry = {"sample": sample, "ids": ids, "both": both, "norms": norms}
         e = self._entry
-        b = query.size(0)
-        tail, _ = knn_tile.prepare(query, want_norms=False)
-        both = torch.cat([e["rows"], tail], 0)
-        norms = None if e["norms"] is None else torch.cat([e["norms"], torch.zeros(b, dtype=torch.float32, device=query.device)])
-        picks = knn_tile.proposals(both, norms, (sample, sample + b), (0, sample), 1)      # indices into the sample
+        knn_tile.prepare(query, want_norms=False, out=e["both"][sample:sample + b])
+        picks = knn_tile.proposals(e["both"], e["norms"], (sample, sample + b), (0, sample), 1)   # indices into the sample
         valid = picks != MAXINT
         return torch.where(valid, e["ids"][picks.clamp(max=sample - 1).long()], picks).contiguous()
 

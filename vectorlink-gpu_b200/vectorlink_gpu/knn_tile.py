@@ -29,13 +29,18 @@ PER_SEGMENT = TILE_K * TILE_LISTS
 BLOCK_K = 64           # the bf16 copy is padded to a multiple of this many columns
 
 
-def prepare(vectors: Tensor, want_norms: bool) -> Tuple[Tensor, Optional[Tensor]]:
-    """bf16 copy of the rows, zero-padded to a multiple of 64 columns, and |row|^2 (fp32) when asked."""
+def prepare(vectors: Tensor, want_norms: bool, out: Optional[Tensor] = None) -> Tuple[Tensor, Optional[Tensor]]:
+    """bf16 copy of the rows, zero-padded to a multiple of 64 columns, and |row|^2 (fp32) when asked.
+    `out` (optional): a contiguous bf16 [rows, padded columns] tensor to write the copy into."""
     _lib.require_cuda(vectors)
     assert vectors.dtype == torch.float32 and vectors.is_contiguous()
     (n, dim) = vectors.size()
     dim_pad = (dim + BLOCK_K - 1) // BLOCK_K * BLOCK_K
-    rows_bf16 = torch.empty((n, dim_pad), dtype=torch.bfloat16, device=vectors.device)
+    if out is None:
+        rows_bf16 = torch.empty((n, dim_pad), dtype=torch.bfloat16, device=vectors.device)
+    else:
+        rows_bf16 = out
+        assert rows_bf16.dtype == torch.bfloat16 and rows_bf16.is_contiguous() and tuple(rows_bf16.shape) == (n, dim_pad)
     norms = torch.empty(n, dtype=torch.float32, device=vectors.device) if want_norms else None
     check(lib().vl_knn_prepare(ptr(vectors), ctypes.c_int64(n), dim, ptr(rows_bf16), dim_pad, ptr(norms),
                                stream_of(vectors)), "vl_knn_prepare")

@@ -187,8 +187,7 @@ class ShardedANN:
                     tile_state["norms"] = torch.cat([norms, torch.zeros(chunk_rows, dtype=norms.dtype, device=norms.device)])
             both = tile_state["both"]
             b = rows.size(0)
-            tail, _ = knn_tile.prepare(rows.contiguous(), want_norms=False)
-            both[n_loc:n_loc + b] = tail
+            knn_tile.prepare(rows.contiguous(), want_norms=False, out=both[n_loc:n_loc + b])
             got = knn_tile.proposals(both, tile_state.get("norms"), (n_loc, n_loc + b), (0, n_loc), 1)
             d = calculate_distances(local, got, metric=metric, queries=rows.contiguous())
             sort_pairs_(got, d, dedup=True)
