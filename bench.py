@@ -303,6 +303,7 @@ def main():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--vectors", dest="n", type=int, default=0, help="override the vector count (per GPU)")
     ap.add_argument("--sample", type=int, default=0, help="vectors in the CPU baseline sample")
+    ap.add_argument("--queries", type=int, default=0, help="override the number of search queries")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--loops", type=int, default=0, help="override optimization_loops")
     ap.add_argument("--quick", action="store_true", help="skip the host-buffer pass and the recall evaluation")
@@ -320,6 +321,8 @@ def main():
     w = dict(WORKLOADS[name])
     if args.n:
         w["n"] = args.n
+    if args.queries:
+        w["queries"] = args.queries
     if args.impl == "reference":
         run_reference(args, w, name)
         return
