@@ -174,23 +174,46 @@ __device__ __noinline__ bool merge_chunk(vl_key_t*& cur, vl_key_t*& nxt, int len
         vl_key_t* t = cur; cur = nxt; nxt = t;
         return true;
     }
-    // several new keys: order them, drop repeats among them, splice by rank
-    vl_key_t k = warp_sort32(want ? key : kNone, lane);
-    bool valid = (k != kNone);
-    const vl_key_t prev = __shfl_up_sync(0xffffffffu, k, 1);
-    if (lane > 0 && prev == k) valid = false;
-    lo = 0;
-    if (valid) {
-        int hi = len;
+    // several new keys: each needs its rank among them (repeats dropped), then all are spliced in by rank.
+    // Up to kRankByCount entrants (the usual case: a handful per iteration) the rank is counted directly -
+    // one broadcast per entrant - and the positions found above stay valid; more entrants, or a repeated
+    // key among them, go through the 32-key sort.
+    constexpr int kRankByCount = 16;
+    vl_key_t k = key;
+    bool valid = want;
+    int rank = 0, nv = __popc(wmask);
+    bool counted = false;
+    if (nv <= kRankByCount) {
+        bool dup = false;
+        unsigned m = wmask;
 #pragma unroll 1
-        while (lo < hi) {
-            int mid = (lo + hi) >> 1;
-            if (cur[mid] < k) lo = mid + 1; else hi = mid;
+        while (m) {                                   // warp-uniform: one pass per entrant
+            const int src = __ffs(m) - 1;
+            m &= m - 1;
+            const vl_key_t o = __shfl_sync(0xffffffffu, key, src);
+            rank += (want && o < key);
+            dup |= (want && o == key && src < lane);
         }
+        counted = !__any_sync(0xffffffffu, dup);
     }
-    const unsigned vmask = __ballot_sync(0xffffffffu, valid);
-    const int rank = __popc(vmask & ((1u << lane) - 1u));
-    const int nv = __popc(vmask);
+    if (!counted) {
+        k = warp_sort32(want ? key : kNone, lane);
+        valid = (k != kNone);
+        const vl_key_t prev = __shfl_up_sync(0xffffffffu, k, 1);
+        if (lane > 0 && prev == k) valid = false;
+        lo = 0;
+        if (valid) {
+            int hi = len;
+#pragma unroll 1
+            while (lo < hi) {
+                int mid = (lo + hi) >> 1;
+                if (cur[mid] < k) lo = mid + 1; else hi = mid;
+            }
+        }
+        const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+        rank = __popc(vmask & ((1u << lane) - 1u));
+        nv = __popc(vmask);
+    }
     if (valid) mpos[rank] = lo;
     __syncwarp();
     // a list element moves down by the number of entering keys below it (those with pos <= j)
