@@ -360,11 +360,13 @@ beam_search_kernel(const vl_beam_params p, const BeamSmem lay)
                     // An id that enters `seen` now can never enter the visit queue again, and the
                     // search queue only looks at newly gathered ids: from here on its memo entry
                     // only has to say "popped" (an ordered distance above every real one).
+                    // The mark goes into both entries of the id's bucket without reading them first: a load
+                    // here would stall the whole iteration for a memory round trip, while losing the
+                    // bucket's other entry only costs one gather if that id comes back.
                     if (memo && lane < ncopy && node != VL_MAXINT) {
-                        vl_key_t* bk = memo + 2 * (size_t)memo_bucket((uint32_t)node, memo_shift, memo_buckets);
-                        const vl_key_t e0 = bk[0], e1 = bk[1];
-                        if ((uint32_t)e0 == (uint32_t)node) bk[0] = kPopped | (uint32_t)node;
-                        else if ((uint32_t)e1 == (uint32_t)node) bk[1] = kPopped | (uint32_t)node;
+                        ulonglong2* bk = reinterpret_cast<ulonglong2*>(memo + 2 * (size_t)memo_bucket((uint32_t)node, memo_shift, memo_buckets));
+                        const vl_key_t mark = kPopped | (uint32_t)node;
+                        *bk = make_ulonglong2(mark, mark);
                     }
                 }
 #pragma unroll 1
