@@ -769,7 +769,13 @@ class ANN:
 
             def seeded_queue():
                 q = Queue(query.size(0), queue_size, queue_size + extra_capacity, device=self.vectors.device)
-                q.insert(seeds[:, :extra_capacity].contiguous(), d[:, :extra_capacity].contiguous())
+                if seeds.size(1) <= extra_capacity:
+                    q.insert(seeds, d)
+                else:       # the best Q distinct (distance, id) pairs of all seeds, as inserting them piecewise would leave
+                    (si, sd) = (seeds.clone(), d.clone())
+                    sort_pairs_(si, sd, dedup=True)
+                    q.indices.narrow(1, 0, queue_size).copy_(si.narrow(1, 0, queue_size))
+                    q.distances.narrow(1, 0, queue_size).copy_(sd.narrow(1, 0, queue_size))
                 return q
 
             if not fused_ok:
@@ -827,6 +833,8 @@ class ANN:
             self._entry = {"sample": sample, "ids": ids, "both": both, "norms": norms}
         e = self._entry
         knn_tile.prepare(query, want_norms=False, out=e["both"][sample:sample + b])
+        # (one segment: more segments would occupy more SMs on a small batch, but their extra picks cost more
+        # in exact distances and sorting than the pass gains - measured)
         picks = knn_tile.proposals(e["both"], e["norms"], (sample, sample + b), (0, sample), 1)   # indices into the sample
         valid = picks != MAXINT
         return torch.where(valid, e["ids"][picks.clamp(max=sample - 1).long()], picks).contiguous()
