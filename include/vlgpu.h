@@ -39,7 +39,7 @@ extern "C" {
 /* Text of the last rejected call on this host thread. */
 const char* vl_last_error(void);
 
-/* Version of this ABI (bumped when a signature changes). */
+/* Version of this ABI (bumped when a signature or the layout of an output changes). */
 int vl_abi_version(void);
 
 /* calculate_distances (kernels.py:174-201, kernel 130-171), generalised to a separate query
@@ -145,17 +145,19 @@ int vl_connected_components(const int32_t* ids, const float* dist, int64_t n, in
  *
  * vl_knn_tile: proposals for every row in [row_lo, row_hi).  The candidate range
  * [cand_lo, cand_hi) is cut into `segments` equal parts (each a multiple of 256 candidates, the
- * tile width), and within a part the tiles alternate between VL_KNN_TILE_LISTS = 2 lists: list 0
- * takes the part's tiles 0, 2, 4, ..., list 1 the tiles 1, 3, 5, ...  Each list holds the ids of
- * the VL_KNN_TILE_K candidates of its tiles with the smallest approximate score - bf16 inner
+ * tile width), and a part's candidates fall into VL_KNN_TILE_LISTS = 4 classes by their position
+ * in their tile: class k takes the 64 candidates [64 k, 64 k + 64) of every 256-candidate tile,
+ * i.e. candidate c of a part that starts at c0 belongs to class ((c - c0) / 64) % 4.  There is one
+ * list per class, and it holds the ids of the VL_KNN_TILE_K candidates of the class with the
+ * smallest approximate score - bf16 inner
  * products accumulated in fp32 on the tensor cores (tcgen05.mma, operands staged by TMA), score =
  * sqnorm[c] - 2<q, c> (squared L2) or -2<q, c> when sqnorm == NULL (cosine).  The row itself is
  * never proposed.  out_ids [row_hi - row_lo, segments, VL_KNN_TILE_LISTS, VL_KNN_TILE_K], best
  * first within a list, MAXINT-padded.  The ids are PROPOSALS: the caller re-evaluates them with
  * vl_calculate_distances and orders them with vl_sort_pairs, so no bf16 value reaches a graph.
  * A wait inside the kernel that runs out sets VL_STATUS_TIMEOUT in *status. */
-#define VL_KNN_TILE_K 32
-#define VL_KNN_TILE_LISTS 2
+#define VL_KNN_TILE_K 16
+#define VL_KNN_TILE_LISTS 4
 int vl_knn_prepare(const float* vectors, int64_t n, int dim, uint16_t* bf16_out, int dim_pad, float* sqnorm_out,
                    void* stream);
 int vl_knn_tile(const uint16_t* rows_bf16, int64_t n, int dim_pad, const float* sqnorm, int64_t row_lo, int64_t row_hi,

@@ -45,7 +45,7 @@ def test_struct_mirror_has_the_size_of_the_c_struct(tmp_path, built_lib):
 def test_rejected_call_reports_an_error_text(built_lib):
     from vectorlink_gpu import _lib
     lib = _lib.lib()
-    assert lib.vl_abi_version() == 3
+    assert lib.vl_abi_version() == 4
     rc = lib.vl_sort_pairs(None, None, 1, 8, 0, None)
     assert rc != 0 and b"null" in lib.vl_last_error()
 

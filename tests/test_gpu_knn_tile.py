@@ -47,9 +47,11 @@ def test_prepare_rounds_to_bf16_pads_and_sums_squares(built_lib):
 @pytest.mark.parametrize("count,segments,rows", [(1000, 1, (0, 1000)), (2500, 3, (300, 1700)), (130, 2, (0, 130)), (700, 2, (5, 650))])
 def test_proposals_are_the_exact_top_of_every_list_on_integer_data(count, segments, rows, built_lib):
     """Integer-valued rows below 256 are exact in bf16 and their inner products are exact in the fp32
-    accumulator, so every list must hold exactly the 32 nearest (squared L2, ties by id) of its
-    candidates - the even or the odd 256-candidate tiles of its segment - the row itself left out."""
-    from vectorlink_gpu.knn_tile import prepare, proposals
+    accumulator, so every list must hold exactly the 16 nearest (squared L2, ties by id) of its
+    candidates - one of the four 64-candidate quarters of every 256-candidate tile of its segment -
+    the row itself left out."""
+    from vectorlink_gpu.knn_tile import TILE_K, TILE_LISTS, prepare, proposals
+    assert (TILE_K, TILE_LISTS) == (16, 4)
     rng = np.random.default_rng(count)
     v = sift_like(rng, count)
     rows_bf16, norms = prepare(t(v), want_norms=True)
@@ -63,18 +65,18 @@ def test_proposals_are_the_exact_top_of_every_list_on_integer_data(count, segmen
     ids = np.arange(count)
     for s in range(segments):
         lo, hi = s * seg_len, min(count, (s + 1) * seg_len)
-        for parity in (0, 1):
-            part = got[:, (2 * s + parity) * 32:(2 * s + parity + 1) * 32]
-            members = ids[(ids >= lo) & (ids < hi) & ((((ids - lo) // 256) & 1) == parity)]
+        for cls in range(TILE_LISTS):
+            part = got[:, (TILE_LISTS * s + cls) * TILE_K:(TILE_LISTS * s + cls + 1) * TILE_K]
+            members = ids[(ids >= lo) & (ids < hi) & ((((ids - lo) // 64) % TILE_LISTS) == cls)]
             if len(members) == 0:
                 assert (part == MAXINT).all()
                 continue
             dm = d[:, members]
-            order = members[np.lexsort((np.broadcast_to(members, dm.shape), dm), axis=1)[:, :32]]
+            order = members[np.lexsort((np.broadcast_to(members, dm.shape), dm), axis=1)[:, :TILE_K]]
             finite = np.take_along_axis(d, order, 1) < np.inf      # a short list may reach the row itself
             for r in range(got.shape[0]):
                 want = order[r][finite[r]]
-                assert np.array_equal(part[r, :len(want)], want), (s, parity, r)
+                assert np.array_equal(part[r, :len(want)], want), (s, cls, r)
                 assert (part[r, len(want):] == MAXINT).all()
 
 

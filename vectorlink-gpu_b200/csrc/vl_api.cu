@@ -33,4 +33,4 @@ int vl_sm_count()
 
 extern "C" const char* vl_last_error(void) { return g_error; }
 
-extern "C" int vl_abi_version(void) { return 3; }
+extern "C" int vl_abi_version(void) { return 4; }

@@ -20,17 +20,22 @@
 //                      (256 columns each: all of TMEM), tcgen05.commit releases the stage /
 //                      publishes the tile.  (N=128 tiles measured 17 % slower: the row operand is
 //                      fetched from shared memory once per instruction whatever N is);
-//   warps 2..9       : two groups of four.  Group g owns accumulator g, i.e. every second candidate
-//                      tile of a segment, and keeps its own lists, so a row ends up with two lists
-//                      per segment (the best of the even tiles and the best of the odd tiles) and
-//                      two warps per scheduler hide each other's latencies.  A warp reads
-//                      its quarter of the accumulator's 128 lanes with tcgen05.ld (one
-//                      row per thread, the next 32 columns in flight while 32 are examined),
-//                      turn inner products into scores and keep each row's 32 best (score, id)
-//                      keys in shared memory, one key per lane: three instructions per column
-//                      mark the few that beat the row's worst key, and each of those is inserted
-//                      by the whole warp with one ballot and one shuffle; the accumulator is
-//                      handed back as soon as it is read, so the next tile's MMAs overlap this.
+//   warps 2..17      : selection, one warp per (quarter of the tile's rows, column class).  Class c is
+//                      columns [64 c, 64 c + 64) of every tile, so all sixteen warps examine a tile at
+//                      once while the MMAs of the next tile fill the other accumulator, and a row
+//                      ends up with four lists per segment (the 16 best of each class).  A warp
+//                      reads its quarter of the accumulator's 128 lanes with tcgen05.ld (one row per
+//                      thread, 32 columns per instruction), turns inner products into scores
+//                      and keeps each row's 16 best (score, id) keys in shared memory, one key per
+//                      lane.  The common path costs one instruction per column: two scores per packed
+//                      FMA, the minimum of eight scores by 3-input min, one compare; only groups of
+//                      eight columns in which some row beats its worst key are looked at column by
+//                      column, and each such (row, column) is inserted by the warp with one ballot
+//                      and one shuffle.  The accumulator is handed back as soon as the tile's last
+//                      columns are in registers.  (Measured on 1M x 128 rows: two groups of four warps
+//                      that own one accumulator each, i.e. alternate tiles: 0.48 s; eight warps on
+//                      every tile, two classes: 0.42 s; sixteen warps, four classes: 0.36 s; with the
+//                      packed / min3 common path: 0.33 s; the MMA and TMA side alone: 0.21 s.)
 // No load uses cluster multicast, no thread-block cluster is launched.
 //
 // Every wait (mbarrier phases) is bounded by wall time: when a wait runs out the kernel sets
@@ -49,8 +54,10 @@ constexpr int kBlockK = 64;                    // bf16 elements per k-block = on
 constexpr int kMaxStages = 4;                  // barrier slots (3 stages in use)
 constexpr int kResidentKBlocks = 2;            // row tiles of up to 2 k-blocks (128 columns) stay in shared memory
 constexpr int kTopK = VL_KNN_TILE_K;           // keys per list
-constexpr int kLists = VL_KNN_TILE_LISTS;      // lists per row and segment: one per selection group
-constexpr int kThreads = 320;                  // warp 0 producer, warp 1 MMA, warps 2-9 selection (two groups of four)
+constexpr int kLists = VL_KNN_TILE_LISTS;      // lists per row and segment: one per column class of a tile
+constexpr int kSelCols = kTileCands / kLists;  // class c = columns [c * kSelCols, (c + 1) * kSelCols) of every tile
+constexpr int kSelWarps = 4 * kLists;          // one selection warp per (quarter of the rows, column class)
+constexpr int kThreads = 64 + 32 * kSelWarps;  // warp 0 producer, warp 1 MMA, warps 2-17 selection
 constexpr uint32_t kTileBytes = kTileRows * kBlockK * 2;              // 16 KB: one k-block of the row tile
 constexpr uint32_t kCandBytes = kTileCands * kBlockK * 2;             // 32 KB: one k-block of a candidate tile
 // operand region, 144 KB: resident mode = 3 candidate stages of 32 KB + the row tile's 2 k-blocks;
@@ -65,11 +72,11 @@ constexpr uint32_t kOffBars = kOperandBytes;
 // full[4] empty[4] tfull[2] tempty[2] drain rows_full rows_empty
 constexpr uint32_t kOffSlot = kOffBars + 8 * (2 * kMaxStages + 7);     // TMEM base address written by tcgen05.alloc
 constexpr uint32_t kOffAbort = kOffSlot + 4;
-constexpr uint32_t kOffBias = (kOffAbort + 4 + 127) & ~127u;           // [8 warps][128] floats: score offsets of a warp's current tile
-constexpr uint32_t kOffLists = kOffBias + 8 * kTileCands * 4;          // [2 groups][128 rows][32] best keys of the work item
+constexpr uint32_t kOffBias = (kOffAbort + 4 + 127) & ~127u;           // [16 warps][64] floats: score offsets of a warp's columns of the current tile
+constexpr uint32_t kOffLists = kOffBias + kSelWarps * kSelCols * 4;    // [4 classes][128 rows][16] best keys of the work item
 constexpr uint32_t kSmemBytes = kOffLists + kLists * kTileRows * kTopK * 8 + 1024;   // + slack for the alignment
-static_assert(kTopK == 32, "a row's list is held one key per lane");
-static_assert(kLists == 2, "one list per accumulator");
+static_assert(kTopK == 16 && kLists == 4, "a row's list is held one key per lane of a half warp; 64 columns per class");
+static_assert(kSelCols % 32 == 0, "a selection warp examines whole chunks of 32 columns");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -203,6 +210,20 @@ __device__ __forceinline__ uint32_t pick32(const uint32_t (&v)[32], int j)
     return x;
 }
 
+// two scores at once: {b0, b1} - 2 * {v0, v1}, each half an ordinary fp32 fma
+__device__ __forceinline__ void score2(uint32_t v0, uint32_t v1, float b0, float b1, float& s0, float& s1)
+{
+    asm("{\n\t.reg .b64 A, B, C, D;\n\tmov.b64 A, {%2, %3};\n\tmov.b64 B, {%4, %4};\n\tmov.b64 C, {%5, %6};\n\t"
+        "fma.rn.f32x2 D, A, B, C;\n\tmov.b64 {%0, %1}, D;\n\t}"
+        : "=f"(s0), "=f"(s1) : "r"(v0), "r"(v1), "f"(-2.0f), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float min3f(float a, float b, float c)
+{
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // RESIDENT: the row tile (all its k-blocks) is loaded once per work item and only candidate
 // tiles go through the ring; otherwise a ring stage holds one k-block of both operands.
 template <bool RESIDENT>
@@ -230,7 +251,7 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, kSelWarps); }
         mbar_init(bar_drain, 1);
         mbar_init(bar_rows_full, 1);
         mbar_init(bar_rows_empty, 1);
@@ -342,12 +363,12 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant_
         }
     } else if (warp >= 2) {
         // ---------------- selection: one row of the tile per thread ----------------
-        const int group = (warp - 2) >> 2;                         // 0: even tiles of a segment (accumulator 0), 1: odd tiles
+        const int cls = (warp - 2) >> 2;                           // this warp's column class
         const int quarter = warp & 3;                              // the TMEM lanes this warp may read
         const int row_in_tile = quarter * 32 + lane;
-        float* bias_tile = bias_smem + (warp - 2) * kTileCands;
+        float* bias_tile = bias_smem + (warp - 2) * kSelCols;
         const float kInf = __int_as_float(0x7f800000);
-        uint32_t used = 0;                                         // tiles this group's accumulator has held so far
+        uint32_t used0 = 0, used1 = 0;                             // tiles accumulator 0 / 1 has held so far
         bool ok = true;
 #pragma unroll 1
         for (int64_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
@@ -355,119 +376,151 @@ knn_tile_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant_
             const int64_t row = a.row_lo + rt * kTileRows + row_in_tile;
             const int64_t c_begin = a.cand_lo + seg * a.seg_len;
             const int64_t c_end = (c_begin + a.seg_len < a.cand_hi) ? c_begin + a.seg_len : a.cand_hi;
-            // The 32 best keys of each of this warp's 32 rows, ascending, in shared memory: row r's list is
-            // warp_lists[r * 32 + lane], one key per lane, so that an insertion is a warp-wide shift (a few
-            // instructions) instead of a 32-step register sort by the one lane that owns the row.  Each
-            // lane keeps `worst`, the score of its own row's last key (+inf until the list is full).
-            vl_key_t* warp_lists = lists_smem + ((size_t)group * kTileRows + quarter * 32) * kTopK;
+            // The kTopK best keys of each of this warp's 32 rows, ascending, in shared memory: row r's list is
+            // warp_lists[r * kTopK + lane], one key per lane, so that an insertion is a warp-wide shift (a few
+            // instructions) instead of a register sort by the one lane that owns the row.  Each lane keeps
+            // `worst`, the score of its own row's last key (+inf until the list is full).
+            vl_key_t* warp_lists = lists_smem + ((size_t)cls * kTileRows + quarter * 32) * kTopK;
             __syncwarp();
 #pragma unroll
-            for (int r = 0; r < 32; ++r) warp_lists[r * kTopK + lane] = ~0ull;
+            for (int i = 0; i < kTopK; ++i) warp_lists[i * 32 + lane] = ~0ull;
             __syncwarp();
             float worst = kInf;
 
-            // Examines 32 accumulator columns: three instructions per column on the common path (score,
-            // compare, mark); when no lane marked anything the chunk is done.  Otherwise every marked
-            // (row, column) is inserted into its row's list by the whole warp.
+            // Examines 32 accumulator columns.  Common path, one instruction per column: per group of 8 columns
+            // four packed FMAs make the scores, 3-input minima reduce them to the smallest, one compare tells
+            // whether this row has anything below its worst key there.  Only the groups in which some row of
+            // the warp has (usually none or one) are looked at column by column, and every (row, column)
+            // that qualifies is inserted into its row's list by the whole warp.
             auto examine = [&](const uint32_t (&v)[32], const float* bias32, int64_t col0) {
-                // four independent partial masks: the chain of dependent instructions has to stay short
-                uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
+                uint32_t sub = 0;
 #pragma unroll
-                for (int j4 = 0; j4 < 32; j4 += 4) {
-                    const float4 b4 = *reinterpret_cast<const float4*>(bias32 + j4);
-                    m0 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 0]), b4.x) < worst) ? (1u << (j4 + 0)) : 0u;
-                    m1 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 1]), b4.y) < worst) ? (1u << (j4 + 1)) : 0u;
-                    m2 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 2]), b4.z) < worst) ? (1u << (j4 + 2)) : 0u;
-                    m3 |= (fmaf(-2.0f, __uint_as_float(v[j4 + 3]), b4.w) < worst) ? (1u << (j4 + 3)) : 0u;
+                for (int s8 = 0; s8 < 4; ++s8) {
+                    const float4 c0 = *reinterpret_cast<const float4*>(bias32 + 8 * s8);
+                    const float4 c1 = *reinterpret_cast<const float4*>(bias32 + 8 * s8 + 4);
+                    float s0, s1, s2, s3, s4, s5, s6, s7;
+                    score2(v[8 * s8 + 0], v[8 * s8 + 1], c0.x, c0.y, s0, s1);
+                    score2(v[8 * s8 + 2], v[8 * s8 + 3], c0.z, c0.w, s2, s3);
+                    score2(v[8 * s8 + 4], v[8 * s8 + 5], c1.x, c1.y, s4, s5);
+                    score2(v[8 * s8 + 6], v[8 * s8 + 7], c1.z, c1.w, s6, s7);
+                    const float m = fminf(min3f(min3f(s0, s1, s2), min3f(s3, s4, s5), s6), s7);
+                    sub |= (m < worst) ? (1u << s8) : 0u;
                 }
-                const uint32_t marks = (m0 | m1) | (m2 | m3);
-                // columns marked by any row of the warp (usually none, one or two): the loop below is over
-                // those only, and is kept rolled so that the code stays small
-                uint32_t cols = __reduce_or_sync(0xffffffffu, marks);
+                uint32_t any = __reduce_or_sync(0xffffffffu, sub);
 #pragma unroll 1
-                while (cols) {
-                    const int j = __ffs(cols) - 1;                  // the same for every lane
-                    cols &= cols - 1;
-                    const float score = fmaf(-2.0f, __uint_as_float(pick32(v, j)), bias32[j]);
-                    const vl_key_t my_key = ((vl_key_t)vl_ord(score) << 32) | (uint32_t)(col0 + j);
-                    // `worst` may have fallen since the marks were taken; a row never lists itself
-                    unsigned live = __ballot_sync(0xffffffffu, ((marks >> j) & 1u) && score < worst && col0 + j != row);
+                while (any) {
+                    const int s8 = __ffs(any) - 1;                  // the same for every lane
+                    any &= any - 1;
+                    uint32_t mk = 0;
+#define VL_MARKS8(B) { \
+                        const float4 c0 = *reinterpret_cast<const float4*>(bias32 + (B)); \
+                        const float4 c1 = *reinterpret_cast<const float4*>(bias32 + (B) + 4); \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 0]), c0.x) < worst) ? 1u : 0u; \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 1]), c0.y) < worst) ? 2u : 0u; \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 2]), c0.z) < worst) ? 4u : 0u; \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 3]), c0.w) < worst) ? 8u : 0u; \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 4]), c1.x) < worst) ? 16u : 0u; \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 5]), c1.y) < worst) ? 32u : 0u; \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 6]), c1.z) < worst) ? 64u : 0u; \
+                        mk |= (fmaf(-2.0f, __uint_as_float(v[(B) + 7]), c1.w) < worst) ? 128u : 0u; }
+                    switch (s8) {
+                        case 0: VL_MARKS8(0) break;
+                        case 1: VL_MARKS8(8) break;
+                        case 2: VL_MARKS8(16) break;
+                        default: VL_MARKS8(24) break;
+                    }
+#undef VL_MARKS8
+                    uint32_t cols = __reduce_or_sync(0xffffffffu, mk);
 #pragma unroll 1
-                    while (live) {
-                        const int owner = __ffs(live) - 1;
-                        live &= live - 1;
-                        const vl_key_t key = __shfl_sync(0xffffffffu, my_key, owner);
-                        vl_key_t* lst = warp_lists + owner * kTopK;
-                        const vl_key_t e = lst[lane];
-                        const int pos = __popc(__ballot_sync(0xffffffffu, e < key));    // sorted: the smaller keys are a prefix
-                        const vl_key_t prev = __shfl_up_sync(0xffffffffu, e, 1);
-                        const vl_key_t ne = lane < pos ? e : (lane == pos ? key : prev);
-                        lst[lane] = ne;
-                        const vl_key_t tail = __shfl_sync(0xffffffffu, ne, 31);
-                        if (lane == owner && tail != ~0ull) worst = vl_unord((uint32_t)(tail >> 32));
-                        __syncwarp();
+                    while (cols) {
+                        const int jj = __ffs(cols) - 1;
+                        cols &= cols - 1;
+                        const int j = 8 * s8 + jj;
+                        const float score = fmaf(-2.0f, __uint_as_float(pick32(v, j)), bias32[j]);
+                        const vl_key_t my_key = ((vl_key_t)vl_ord(score) << 32) | (uint32_t)(col0 + j);
+                        unsigned live = __ballot_sync(0xffffffffu, ((mk >> jj) & 1u) && score < worst && col0 + j != row);
+#pragma unroll 1
+                        while (live) {
+                            const int owner = __ffs(live) - 1;
+                            live &= live - 1;
+                            const vl_key_t key = __shfl_sync(0xffffffffu, my_key, owner);
+                            vl_key_t* lst = warp_lists + owner * kTopK;
+                            const vl_key_t e = lane < kTopK ? lst[lane] : ~0ull;
+                            const int pos = __popc(__ballot_sync(0xffffffffu, e < key));
+                            const vl_key_t prev = __shfl_up_sync(0xffffffffu, e, 1);
+                            const vl_key_t ne = lane < pos ? e : (lane == pos ? key : prev);
+                            if (lane < kTopK) lst[lane] = ne;
+                            const vl_key_t tail = __shfl_sync(0xffffffffu, ne, kTopK - 1);
+                            if (lane == owner && tail != ~0ull) worst = vl_unord((uint32_t)(tail >> 32));
+                            __syncwarp();
+                        }
                     }
                 }
             };
-
-            // score offsets of a tile, four columns per lane: |c|^2 (squared L2) or 0 (cosine), +inf past the
+            // score offsets of this warp's columns of a tile: |c|^2 (squared L2) or 0 (cosine), +inf past the
             // segment's end so that such a column never qualifies
-            auto load_bias = [&](int64_t c0, float (&b)[kTileCands / 32]) {
+            auto load_bias = [&](int64_t c0, float (&b)[kSelCols / 32]) {
 #pragma unroll
-                for (int q = 0; q < kTileCands / 32; ++q) {
+                for (int q = 0; q < kSelCols / 32; ++q) {
                     const int64_t c = c0 + lane + 32 * q;
                     b[q] = (c < c_end) ? (a.bias ? __ldg(a.bias + c) : 0.0f) : kInf;
                 }
             };
-            float next_bias[kTileCands / 32];
-            const int64_t c_first = c_begin + (int64_t)group * kTileCands;
-            if (c_first < c_end) load_bias(c_first, next_bias);
+            float next_bias[kSelCols / 32];
+            const int64_t c_off = (int64_t)cls * kSelCols;
+            if (c_begin < c_end) load_bias(c_begin + c_off, next_bias);
+            uint32_t lt = 0;
 #pragma unroll 1
-            for (int64_t c0 = c_first; c0 < c_end; c0 += 2 * kTileCands) {
+            for (int64_t c0 = c_begin; c0 < c_end; c0 += kTileCands, ++lt) {
                 // this warp's own copy of the offsets (warp-local: this role uses no CTA-wide barrier); the
                 // next tile's offsets are requested now and stored when this tile is done
                 __syncwarp();
 #pragma unroll
-                for (int q = 0; q < kTileCands / 32; ++q) bias_tile[lane + 32 * q] = next_bias[q];
+                for (int q = 0; q < kSelCols / 32; ++q) bias_tile[lane + 32 * q] = next_bias[q];
                 __syncwarp();
-                if (c0 + 2 * kTileCands < c_end) load_bias(c0 + 2 * kTileCands, next_bias);
-                const uint32_t tph = used & 1u;
-                ++used;
-                { VL_T0(); ok = mbar_wait(bar_tfull + 8 * group, tph, abort_flag, a.status); if (lane == 0 && warp == 2) VL_T1(3); }
+                if (c0 + kTileCands < c_end) load_bias(c0 + kTileCands + c_off, next_bias);
+                const uint32_t buf = lt & 1u;
+                const uint32_t tph = (buf ? used1 : used0) & 1u;
+                if (buf) ++used1; else ++used0;
+                { VL_T0(); ok = mbar_wait(bar_tfull + 8 * buf, tph, abort_flag, a.status); if (lane == 0 && warp == 2) VL_T1(3); }
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + group * kTileCands;
-                uint32_t v0[32], v1[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kTileCands + cls * kSelCols;
                 VL_T0();
-                tc_load32(taddr, v0);
-                tc_wait_ld();
-                if (lane == 0 && warp == 2) VL_T1(4);
+                {
+                    // four warps per scheduler hide each other's latencies: one chunk of 32 columns at a time
+                    uint32_t v0[32];
 #pragma unroll 1
-                for (int ch = 0; ch < kTileCands / 32; ch += 2) {
-                    __syncwarp();                                   // the loads are warp-collective
-                    tc_load32(taddr + (ch + 1) * 32, v1);           // in flight while v0 is examined
-                    examine(v0, bias_tile + ch * 32, c0 + ch * 32);
+                    for (int ch = 0; ch < kSelCols / 32; ++ch) {
+                        __syncwarp();
+                        tc_load32(taddr + ch * 32, v0);
+                        tc_wait_ld();
+                        if (ch + 1 == kSelCols / 32) {
+                            // the tile's last columns are in registers: hand the accumulator back now, the
+                            // next tile's MMAs run while this chunk is examined
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                        }
+                        examine(v0, bias_tile + ch * 32, c0 + c_off + ch * 32);
+                    }
                     __syncwarp();
-                    tc_wait_ld();
-                    if (ch + 2 < kTileCands / 32) tc_load32(taddr + (ch + 2) * 32, v0);
-                    examine(v1, bias_tile + (ch + 1) * 32, c0 + (ch + 1) * 32);
-                    __syncwarp();
-                    tc_wait_ld();
                 }
                 if (lane == 0 && warp == 2) { VL_T1(5); if (a.stats) atomicAdd(a.stats + 6, 1ull); }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tempty + 8 * group);  // 4 warps -> accumulator free again
             }
-            if (ok) {      // the warp writes its rows' lists, one row (32 ids = 128 bytes) per step
+            if (ok) {      // the warp writes its rows' lists, 32 ids = 128 bytes per step
                 __syncwarp();
                 const int64_t first_row = a.row_lo + rt * kTileRows + quarter * 32;
+                constexpr int kRowsPerStep = 32 / kTopK;
 #pragma unroll 1
-                for (int r = 0; r < 32 && first_row + r < a.row_hi; ++r) {
-                    const vl_key_t k = warp_lists[r * kTopK + lane];
-                    a.out_ids[(((first_row + r - a.row_lo) * a.segments + seg) * kLists + group) * kTopK + lane] =
-                        k == ~0ull ? VL_MAXINT : (int32_t)(uint32_t)k;
+                for (int r0 = 0; r0 < 32; r0 += kRowsPerStep) {
+                    const int r = r0 + lane / kTopK, kk = lane % kTopK;
+                    if (first_row + r < a.row_hi) {
+                        const vl_key_t k = warp_lists[r * kTopK + kk];
+                        a.out_ids[(((first_row + r - a.row_lo) * a.segments + seg) * kLists + cls) * kTopK + kk] =
+                            k == ~0ull ? VL_MAXINT : (int32_t)(uint32_t)k;
+                    }
                 }
                 __syncwarp();
             }

@@ -23,8 +23,8 @@ from .constants import MAXFLOAT, MAXINT
 from .kernels import calculate_distances, metric_code, sort_pairs_
 from .log import nvtx_range
 
-TILE_K = 32            # VL_KNN_TILE_K: ids per list
-TILE_LISTS = 2         # VL_KNN_TILE_LISTS: lists per row and candidate segment (even tiles, odd tiles)
+TILE_K = 16            # VL_KNN_TILE_K: ids per list
+TILE_LISTS = 4         # VL_KNN_TILE_LISTS: lists per row and candidate segment (one per 64-candidate quarter of the tiles)
 PER_SEGMENT = TILE_K * TILE_LISTS
 BLOCK_K = 64           # the bf16 copy is padded to a multiple of this many columns
 
@@ -50,8 +50,9 @@ def prepare(vectors: Tensor, want_norms: bool, out: Optional[Tensor] = None) -> 
 def proposals(rows_bf16: Tensor, norms: Optional[Tensor], rows: Tuple[int, int], candidates: Tuple[int, int],
               segments: int) -> Tensor:
     """int32 [rows, segments * 64]: per row and per part of the candidate range (`segments` equal
-    parts) two lists of 32 ids, the best-scoring candidates of the part's even and of its odd
-    256-candidate tiles (approximate scores; the row itself excluded), MAXINT-padded."""
+    parts) four lists of 16 ids: list k holds the best-scoring candidates among the k-th quarters
+    (64 candidates) of the part's 256-candidate tiles (approximate scores; the row itself excluded),
+    MAXINT-padded."""
     _lib.require_cuda(rows_bf16, norms)
     assert rows_bf16.dtype == torch.bfloat16 and rows_bf16.is_contiguous()
     (n, dim_pad) = rows_bf16.size()
