@@ -511,12 +511,30 @@ def main():
         alt_q = torch.tensor([q0.elapsed_time(q1) / reps], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(alt_q, op=dist.ReduceOp.MAX)
+        # the tile pass alone, timed live (CUDA events, all pairs of this GPU's rows): its roofline is the tensor one
+        tile_pass = None
+        if world == 1 and total <= 2_000_000:          # all pairs: the cost grows with the square of the rows
+            from vectorlink_gpu import knn_tile
+            rows_bf16, norms = knn_tile.prepare(vectors, want_norms=w["metric"] == "l2")
+            knn_tile.proposals(rows_bf16, norms, (0, total), (0, total), 1)
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record()
+            for _ in range(3):
+                knn_tile.proposals(rows_bf16, norms, (0, total), (0, total), 1)
+            p1.record()
+            torch.cuda.synchronize()
+            pass_ms = p0.elapsed_time(p1) / 3
+            tflops = 2.0 * total * total * rows_bf16.size(1) / (pass_ms * 1e-3) / 1e12
+            tile_pass = {"kernel": "knn_tile_kernel", "ms_per_launch": pass_ms, "pairs": float(total) * total,
+                         "dim_padded": rows_bf16.size(1), "bound": "tensor", "achieved": tflops, "unit": "TFLOP/s"}
+            del rows_bf16, norms
         tile_start = {"init": "knn_tile", "optimization_loops": 1, "search_entry_sample": kw_tile["search_entry_sample"],
                       "steps": alt_steps, "ms_per_step": float(alt_ms.item()),
                       "value": total / (float(alt_ms.item()) * 1e-3), "unit": "vectors/s",
                       "graph_recall_at_10": recall_at_k(alt_index.beams[:gsample], gtruth, 10) if want_recall else None,
                       "search_qps": queries.size(0) / (float(alt_q.item()) * 1e-3),
-                      "search_recall_at_10": recall_at_k(alt_found[:n_eval], truth, 10) if want_recall else None}
+                      "search_recall_at_10": recall_at_k(alt_found[:n_eval], truth, 10) if want_recall else None,
+                      "tile_pass": tile_pass}
     status = _lib.read_status(dev)
 
     times = torch.tensor([ms_total, e2e_ms, search_ms], device=dev, dtype=torch.float64)
@@ -533,6 +551,14 @@ def main():
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650"
         ms_per_step = ms_total / args.steps
+        if tile_start and tile_start.get("tile_pass"):
+            tp = tile_start["tile_pass"]
+            tp["peak"] = float(peaks.get("bf16_tflops", 1590.0))
+            tp["peak_sustained"] = float(peaks.get("bf16_tflops_sustained", 1400.0))
+            tp["peak_source"] = ("measured (MEASURED_PEAKS.json bf16_tflops, a burst cuBLAS GEMM)" if "bf16_tflops" in peaks
+                                 else "fallback 1590")
+            tp["frac"] = tp["achieved"] / tp["peak"]
+            tp["frac_of_sustained"] = tp["achieved"] / tp["peak_sustained"]
         line = {
             "metric": "graph_build_vectors_per_s", "value": total / (ms_per_step * 1e-3), "unit": "vectors/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
