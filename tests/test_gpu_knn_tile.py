@@ -80,6 +80,40 @@ def test_proposals_are_the_exact_top_of_every_list_on_integer_data(count, segmen
                 assert (part[r, len(want):] == MAXINT).all()
 
 
+@pytest.mark.parametrize("count,dim,segments,rows,cands", [
+    (5, 128, 1, (0, 5), (0, 5)),            # far less than one tile
+    (40, 96, 4, (0, 40), (0, 40)),          # more segments than tiles: three of them are empty
+    (300, 128, 1, (7, 8), (0, 300)),        # a single row
+    (300, 200, 2, (0, 300), (100, 101)),    # a single candidate; rows streamed (padded dimension 256 > 128)
+    (600, 64, 1, (250, 600), (0, 256)),     # candidates end exactly at a tile edge
+])
+def test_ragged_and_tiny_ranges(count, dim, segments, rows, cands, built_lib):
+    """Every list holds the nearest of its class among the offered candidates, whatever the shape of the ranges."""
+    from vectorlink_gpu.knn_tile import TILE_K, TILE_LISTS, prepare, proposals
+    rng = np.random.default_rng(count + dim)
+    v = sift_like(rng, count, dim, centres=4)
+    rows_bf16, norms = prepare(t(v), want_norms=True)
+    got = n(proposals(rows_bf16, norms, rows, cands, segments))
+    assert status_clear()
+    assert got.shape == (rows[1] - rows[0], segments * TILE_K * TILE_LISTS)
+    span = cands[1] - cands[0]
+    seg_len = ((span + segments - 1) // segments + 255) // 256 * 256
+    d = ((v[rows[0]:rows[1], None, :].astype(np.float64) - v[None, :, :].astype(np.float64)) ** 2).sum(2)
+    d[np.arange(rows[1] - rows[0]), np.arange(rows[0], rows[1])] = np.inf
+    ids = np.arange(count)
+    for s in range(segments):
+        lo, hi = cands[0] + s * seg_len, min(cands[1], cands[0] + (s + 1) * seg_len)
+        for cls in range(TILE_LISTS):
+            part = got[:, (TILE_LISTS * s + cls) * TILE_K:(TILE_LISTS * s + cls + 1) * TILE_K]
+            members = ids[(ids >= lo) & (ids < hi) & ((((ids - lo) // 64) % TILE_LISTS) == cls)]
+            for r in range(got.shape[0]):
+                dm = d[r, members]
+                order = members[np.lexsort((members, dm))][:TILE_K]
+                want = order[d[r, order] < np.inf]
+                assert np.array_equal(part[r, :len(want)], want), (s, cls, r)
+                assert (part[r, len(want):] == MAXINT).all()
+
+
 @pytest.mark.parametrize("dim,metric", [(96, "cosine"), (768, "cosine"), (1024, "cosine"), (128, "l2")])
 def test_start_graph_lists_are_exact_and_cover_the_true_neighbours(dim, metric, built_lib):
     """Unit-norm float rows: the bf16 scores are approximate, the lists are not - every stored
